@@ -1,0 +1,55 @@
+"""ctypes binding of ``libarcq_b200.so`` (the C ABI declared in ``include/arcq_b200.h``).
+
+There is no fallback: if the library is missing or fails to load, importing
+the ops raises with the build command.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = PKG_DIR / "libarcq_b200.so"
+
+DT_F32, DT_F16, DT_BF16 = 0, 1, 2
+
+# every symbol include/arcq_b200.h declares
+EXPORTS = (
+    "arcq_version", "arcq_last_error_string", "arcq_device_status", "arcq_act_quant", "arcq_packed_gemm",
+    "arcq_unpack_codes", "arcq_pack_codes", "arcq_dequant",
+)
+
+_lib = None
+
+
+class ArcqLibraryMissing(ImportError):
+    pass
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once and declare the argument types."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ArcqLibraryMissing(
+            f"{LIB_PATH} is not built. Build it with `python {PKG_DIR / 'build.py'}` "
+            "(needs nvcc with sm_100a support); there is no CPU or PyTorch fallback for this path.")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    vp, i64, ci = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+    lib.arcq_version.restype = ci
+    lib.arcq_last_error_string.restype = ctypes.c_char_p
+    lib.arcq_device_status.restype = ci
+    lib.arcq_act_quant.argtypes = [vp, ci, i64, i64, vp, vp, ci, ci, vp, vp, vp, vp, vp, ci, vp]
+    lib.arcq_packed_gemm.argtypes = [vp] * 11 + [ci, ci, i64, i64, i64, vp, ci, vp]
+    lib.arcq_unpack_codes.argtypes = [vp, i64, i64, ci, vp, vp]
+    lib.arcq_pack_codes.argtypes = [vp, i64, i64, ci, vp, vp]
+    lib.arcq_dequant.argtypes = [vp, vp, vp, vp, vp, ci, ci, i64, i64, vp, ci, vp]
+    for name in EXPORTS:
+        getattr(lib, name)  # AttributeError here means header and library disagree
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().arcq_last_error_string().decode("utf-8", "replace")

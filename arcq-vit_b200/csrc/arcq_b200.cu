@@ -1,0 +1,277 @@
+// C ABI of the B200 back end: argument checks, launch configuration, error reporting.
+// The kernels live in the .cuh files included below; this is the only translation unit.
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "../../include/arcq_b200.h"
+#include "ptx.cuh"
+#include "act_quant.cuh"
+#include "codes.cuh"
+#include "packed_gemm.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(ARCQ_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+__device__ int g_status_word = 0;
+
+int* status_ptr() {
+  // one address per device; looked up once per device and cached
+  static thread_local int cached_dev = -1;
+  static thread_local int* cached = nullptr;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != cached_dev) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    cached = static_cast<int*>(p);
+    cached_dev = dev;
+  }
+  return cached;
+}
+
+int sm_count() {
+  static thread_local int cached_dev = -1;
+  static thread_local int sms = 148;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != cached_dev) {
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cached_dev = dev;
+  }
+  return sms;
+}
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int grid_for(long long work_items, int per_block, int blocks_per_sm) {
+  long long need = (work_items + per_block - 1) / per_block;
+  long long cap = static_cast<long long>(sm_count()) * blocks_per_sm;
+  if (need < 1) need = 1;
+  return static_cast<int>(need < cap ? need : cap);
+}
+
+template <typename T, int BITS>
+cudaError_t launch_act_quant(const void* x, long long groups, const float* th, const float* cb, uint8_t* packed,
+                             float* mu, float* sg, float* cs, void* xhat, int xhat_dtype, cudaStream_t st) {
+  const int grid = grid_for((groups + 3) / 4, 8, 8);
+  const T* xt = static_cast<const T*>(x);
+  if (xhat == nullptr) {
+    arcq::act_quant_kernel<T, BITS, float, false><<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, nullptr);
+  } else if (xhat_dtype == ARCQ_DT_F32) {
+    arcq::act_quant_kernel<T, BITS, float, true>
+        <<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, static_cast<float*>(xhat));
+  } else if (xhat_dtype == ARCQ_DT_F16) {
+    arcq::act_quant_kernel<T, BITS, __half, true>
+        <<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, static_cast<__half*>(xhat));
+  } else {
+    arcq::act_quant_kernel<T, BITS, __nv_bfloat16, true>
+        <<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, static_cast<__nv_bfloat16*>(xhat));
+  }
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t dispatch_act_quant_bits(int bits, const void* x, long long groups, const float* th, const float* cb,
+                                    uint8_t* packed, float* mu, float* sg, float* cs, void* xhat, int xhat_dtype,
+                                    cudaStream_t st) {
+  switch (bits) {
+    case 4: return launch_act_quant<T, 4>(x, groups, th, cb, packed, mu, sg, cs, xhat, xhat_dtype, st);
+    case 3: return launch_act_quant<T, 3>(x, groups, th, cb, packed, mu, sg, cs, xhat, xhat_dtype, st);
+    default: return launch_act_quant<T, 2>(x, groups, th, cb, packed, mu, sg, cs, xhat, xhat_dtype, st);
+  }
+}
+
+// Tile width for the packed GEMM: the widest multiple of 16 (<= 256) that divides N, narrowed while
+// the grid would leave most of the SMs idle.
+int choose_bn(long long M, long long N) {
+  static const int cand[] = {256, 192, 128, 96, 64, 48, 32, 16};
+  const long long tiles_m = (M + arcq::kTileM - 1) / arcq::kTileM;
+  int widest = 0, narrowest = 0;
+  for (int c : cand) {
+    if (N % c != 0) continue;
+    if (widest == 0) widest = c;
+    if (tiles_m * (N / c) >= sm_count()) return c;  // widest tile that still fills the machine
+    if (c >= 32 || narrowest == 0) narrowest = c;
+  }
+  if (widest != 0) return narrowest;
+  const long long r = (N + 15) / 16 * 16;  // N not a multiple of 16: pad the last tile column
+  return static_cast<int>(r < 256 ? r : 256);
+}
+
+}  // namespace
+
+extern "C" {
+
+int arcq_version(void) { return ARCQ_B200_VERSION; }
+
+const char* arcq_last_error_string(void) { return g_err; }
+
+int arcq_device_status(void) {
+  int v = 0, zero = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return fail(ARCQ_E_CUDA, "device synchronize failed: %s",
+                                                          cudaGetErrorString(cudaGetLastError()));
+  if (cudaMemcpyFromSymbol(&v, g_status_word, sizeof(int)) != cudaSuccess) return fail(ARCQ_E_CUDA, "status read failed");
+  if (v != 0) cudaMemcpyToSymbol(g_status_word, &zero, sizeof(int));
+  return v;
+}
+
+int arcq_act_quant(const void* x, int x_dtype, int64_t M, int64_t K, const float* thresholds, const float* codebook,
+                   int bits, int group_size, uint8_t* packed_out, float* mu_out, float* sigma_out, float* codesum_out,
+                   void* xhat_out, int xhat_dtype, void* stream) {
+  if (x == nullptr || thresholds == nullptr || codebook == nullptr) return fail(ARCQ_E_BAD_ARG, "null input pointer");
+  if (packed_out == nullptr && xhat_out == nullptr) return fail(ARCQ_E_BAD_ARG, "no output requested");
+  if ((packed_out != nullptr) != (mu_out != nullptr) || (mu_out != nullptr) != (sigma_out != nullptr))
+    return fail(ARCQ_E_BAD_ARG, "packed_out, mu_out and sigma_out go together");
+  if (codesum_out != nullptr && mu_out == nullptr) return fail(ARCQ_E_BAD_ARG, "codesum_out needs mu_out");
+  if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
+  if (x_dtype < ARCQ_DT_F32 || x_dtype > ARCQ_DT_BF16) return fail(ARCQ_E_BAD_ARG, "bad x_dtype %d", x_dtype);
+  if (xhat_out != nullptr && (xhat_dtype < ARCQ_DT_F32 || xhat_dtype > ARCQ_DT_BF16))
+    return fail(ARCQ_E_BAD_ARG, "bad xhat_dtype %d", xhat_dtype);
+  if (M < 0 || K <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape M=%lld K=%lld", (long long)M, (long long)K);
+  if (group_size <= 0 || K % group_size != 0)
+    return fail(ARCQ_E_BAD_SHAPE, "K=%lld is not a multiple of group_size=%d", (long long)K, group_size);
+  if (group_size != 64) return fail(ARCQ_E_UNSUPPORTED, "group_size %d: only 64 is built", group_size);
+  if (packed_out != nullptr && !aligned(packed_out, 4)) return fail(ARCQ_E_ALIGN, "packed_out must be 4-byte aligned");
+  if (M == 0) return ARCQ_OK;
+  const long long groups = static_cast<long long>(M) * (K / 64);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (x_dtype == ARCQ_DT_F32)
+    e = dispatch_act_quant_bits<float>(bits, x, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
+                                       codesum_out, xhat_out, xhat_dtype, st);
+  else if (x_dtype == ARCQ_DT_F16)
+    e = dispatch_act_quant_bits<__half>(bits, x, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
+                                        codesum_out, xhat_out, xhat_dtype, st);
+  else
+    e = dispatch_act_quant_bits<__nv_bfloat16>(bits, x, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
+                                               codesum_out, xhat_out, xhat_dtype, st);
+  if (e != cudaSuccess) return cuda_fail(e, "act_quant launch");
+  return ARCQ_OK;
+}
+
+int arcq_packed_gemm(const uint8_t* packed_x, const float* mu_a, const float* sigma_a, const float* codesum_a,
+                     const uint8_t* packed_w, const float* mu_w, const float* sigma_w, const float* codesum_w,
+                     const float* act_codebook, const float* w_codebook, const float* bias, int bits, int group_size,
+                     int64_t M, int64_t N, int64_t K, void* y, int y_dtype, void* stream) {
+  if (!packed_x || !mu_a || !sigma_a || !codesum_a || !packed_w || !mu_w || !sigma_w || !codesum_w ||
+      !act_codebook || !w_codebook || !y)
+    return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
+  if (y_dtype != ARCQ_DT_F16 && y_dtype != ARCQ_DT_F32) return fail(ARCQ_E_BAD_ARG, "y_dtype must be f16 or f32");
+  if (M < 0 || N <= 0 || K <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape M=%lld N=%lld K=%lld", (long long)M,
+                                              (long long)N, (long long)K);
+  if (group_size <= 0 || K % group_size != 0)
+    return fail(ARCQ_E_BAD_SHAPE, "K=%lld is not a multiple of group_size=%d", (long long)K, group_size);
+  if (group_size != 64) return fail(ARCQ_E_UNSUPPORTED, "group_size %d: only 64 is built", group_size);
+  if (N % 8 != 0) return fail(ARCQ_E_BAD_SHAPE, "N=%lld must be a multiple of 8", (long long)N);
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > (1 << 20)) return fail(ARCQ_E_TOO_LARGE, "shape too large");
+  if (!aligned(packed_x, 4) || !aligned(packed_w, 4)) return fail(ARCQ_E_ALIGN, "packed codes must be 4-byte aligned");
+  if (!aligned(y, 16)) return fail(ARCQ_E_ALIGN, "y must be 16-byte aligned");
+  if (M == 0) return ARCQ_OK;
+
+  arcq::GemmParams p;
+  p.pa = packed_x; p.mu_a = mu_a; p.sg_a = sigma_a; p.cs_a = codesum_a;
+  p.pw = packed_w; p.mu_w = mu_w; p.sg_w = sigma_w; p.cs_w = codesum_w;
+  p.cb_a = act_codebook; p.cb_w = w_codebook; p.bias = bias; p.y = y;
+  p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K); p.G = static_cast<int>(K / 64);
+  p.pc = static_cast<int>(K * bits / 8);
+  p.bn = choose_bn(M, N);
+  p.y_f32 = (y_dtype == ARCQ_DT_F32) ? 1 : 0;
+  p.status = status_ptr();
+  if (p.status == nullptr) return fail(ARCQ_E_CUDA, "device status word not reachable");
+
+  const size_t smem = arcq::packed_gemm_smem_bytes(p.bn);
+  dim3 grid(static_cast<unsigned>((M + arcq::kTileM - 1) / arcq::kTileM), static_cast<unsigned>((N + p.bn - 1) / p.bn));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaSuccess;
+#define ARCQ_LAUNCH_GEMM(B)                                                                                  \
+  do {                                                                                                       \
+    e = cudaFuncSetAttribute(arcq::packed_gemm_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
+                             static_cast<int>(smem));                                                        \
+    if (e == cudaSuccess) {                                                                                  \
+      arcq::packed_gemm_kernel<B><<<grid, arcq::kGemmThreads, smem, st>>>(p);                                \
+      e = cudaGetLastError();                                                                                \
+    }                                                                                                        \
+  } while (0)
+  if (bits == 4) ARCQ_LAUNCH_GEMM(4);
+  else if (bits == 3) ARCQ_LAUNCH_GEMM(3);
+  else ARCQ_LAUNCH_GEMM(2);
+#undef ARCQ_LAUNCH_GEMM
+  if (e != cudaSuccess) return cuda_fail(e, "packed_gemm launch");
+  return ARCQ_OK;
+}
+
+int arcq_unpack_codes(const uint8_t* packed, int64_t rows, int64_t length, int bits, uint8_t* codes_out, void* stream) {
+  if (!packed || !codes_out) return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
+  if (rows < 0 || length < 0) return fail(ARCQ_E_BAD_SHAPE, "negative shape");
+  if (rows == 0 || length == 0) return ARCQ_OK;
+  const long long pc = (length * bits + 7) / 8;
+  arcq::unpack_codes_kernel<<<grid_for(rows * length, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      packed, rows, length, pc, bits, codes_out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "unpack launch");
+  return ARCQ_OK;
+}
+
+int arcq_pack_codes(const uint8_t* codes, int64_t rows, int64_t length, int bits, uint8_t* packed_out, void* stream) {
+  if (!codes || !packed_out) return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
+  if (rows < 0 || length < 0) return fail(ARCQ_E_BAD_SHAPE, "negative shape");
+  if (rows == 0 || length == 0) return ARCQ_OK;
+  const long long pc = (length * bits + 7) / 8;
+  arcq::pack_codes_kernel<<<grid_for(rows * pc, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      codes, rows, length, pc, bits, packed_out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "pack launch");
+  return ARCQ_OK;
+}
+
+int arcq_dequant(const uint8_t* packed, const float* mu, const float* sigma, const float* codesum, const float* codebook,
+                 int bits, int group_size, int64_t rows, int64_t K, void* out, int out_dtype, void* stream) {
+  if (!packed || !mu || !sigma || !codesum || !codebook || !out) return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
+  if (out_dtype != ARCQ_DT_F16 && out_dtype != ARCQ_DT_F32) return fail(ARCQ_E_BAD_ARG, "out_dtype must be f16 or f32");
+  if (rows < 0 || K <= 0 || group_size <= 0 || K % group_size != 0 || group_size % 8 != 0)
+    return fail(ARCQ_E_BAD_SHAPE, "bad shape rows=%lld K=%lld group_size=%d", (long long)rows, (long long)K, group_size);
+  if (!aligned(packed, 4)) return fail(ARCQ_E_ALIGN, "packed codes must be 4-byte aligned");
+  if (rows == 0) return ARCQ_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(rows * (K / 8), 256, 8);
+  const int k = static_cast<int>(K);
+#define ARCQ_LAUNCH_DQ(B)                                                                                          \
+  do {                                                                                                             \
+    if (out_dtype == ARCQ_DT_F32)                                                                                  \
+      arcq::dequant_kernel<B, float><<<grid, 256, 0, st>>>(packed, mu, sigma, codesum, codebook, rows, k,          \
+                                                           group_size, static_cast<float*>(out));                 \
+    else                                                                                                           \
+      arcq::dequant_kernel<B, __half><<<grid, 256, 0, st>>>(packed, mu, sigma, codesum, codebook, rows, k,         \
+                                                            group_size, static_cast<__half*>(out));               \
+  } while (0)
+  if (bits == 4) ARCQ_LAUNCH_DQ(4);
+  else if (bits == 3) ARCQ_LAUNCH_DQ(3);
+  else ARCQ_LAUNCH_DQ(2);
+#undef ARCQ_LAUNCH_DQ
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "dequant launch");
+  return ARCQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,104 @@
+// Bit-stream helpers and the small format kernels (unpack, pack, reconstruct).
+// Layout: code j of a row occupies bits [j*bits, (j+1)*bits) of the row's little-endian bit stream.
+#pragma once
+#include <cuda_fp16.h>
+#include "ptx.cuh"
+#include "act_quant.cuh"
+
+namespace arcq {
+
+// Inverse of squeeze_nibbles_3/2: spread 8 packed codes into one nibble each.
+__device__ __forceinline__ uint32_t spread_3_to_nibbles(uint32_t v24) {
+  uint32_t u = (v24 & 0xFFFu) | ((v24 & 0xFFF000u) << 4);
+  uint32_t t = (u & 0x003F003Fu) | ((u & 0x0FC00FC0u) << 2);
+  return (t & 0x07070707u) | ((t & 0x38383838u) << 1);
+}
+__device__ __forceinline__ uint32_t spread_2_to_nibbles(uint32_t v16) {
+  uint32_t u = (v16 & 0xFFu) | ((v16 & 0xFF00u) << 8);
+  uint32_t t = (u & 0x000F000Fu) | ((u & 0x00F000F0u) << 4);
+  return (t & 0x03030303u) | ((t & 0x0C0C0C0Cu) << 2);
+}
+
+// The 8 codes of chunk `chunk` (elements 8*chunk .. 8*chunk+7) of a packed row, one per nibble.
+// Reads exactly the bytes that hold those codes, never past the row.
+template <int BITS>
+__device__ __forceinline__ uint32_t load_codes8(const uint8_t* __restrict__ row, int chunk) {
+  if (BITS == 4) {
+    return __ldg(reinterpret_cast<const uint32_t*>(row) + chunk);
+  } else if (BITS == 3) {
+    const uint8_t* p = row + 3 * chunk;
+    const uint32_t v = static_cast<uint32_t>(__ldg(p)) | (static_cast<uint32_t>(__ldg(p + 1)) << 8) |
+                       (static_cast<uint32_t>(__ldg(p + 2)) << 16);
+    return spread_3_to_nibbles(v);
+  } else {
+    return spread_2_to_nibbles(__ldg(reinterpret_cast<const uint16_t*>(row) + chunk));
+  }
+}
+
+__global__ void unpack_codes_kernel(const uint8_t* __restrict__ packed, long long rows, long long length,
+                                    long long packed_cols, int bits, uint8_t* __restrict__ out) {
+  const long long total = rows * length;
+  const unsigned mask = (1u << bits) - 1u;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / length, j = i - r * length;
+    const long long bit = j * bits;
+    const uint8_t* p = packed + r * packed_cols + (bit >> 3);
+    const int sh = static_cast<int>(bit & 7);
+    unsigned v = static_cast<unsigned>(p[0]) >> sh;
+    if (sh + bits > 8) v |= static_cast<unsigned>(p[1]) << (8 - sh);
+    out[i] = static_cast<uint8_t>(v & mask);
+  }
+}
+
+// One thread per output byte: gathers the (at most 5) codes that overlap it.
+__global__ void pack_codes_kernel(const uint8_t* __restrict__ codes, long long rows, long long length,
+                                  long long packed_cols, int bits, uint8_t* __restrict__ out) {
+  const long long total = rows * packed_cols;
+  const unsigned mask = (1u << bits) - 1u;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / packed_cols, b = i - r * packed_cols;
+    const long long bit0 = b * 8;
+    long long j = bit0 / bits;
+    unsigned acc = 0;
+    for (; j < length && j * bits < bit0 + 8; ++j) {
+      const long long cb = j * bits;  // first bit of code j
+      const unsigned c = static_cast<unsigned>(codes[r * length + j]) & mask;
+      acc |= (cb >= bit0) ? (c << (cb - bit0)) : (c >> (bit0 - cb));
+    }
+    out[i] = static_cast<uint8_t>(acc & 0xffu);
+  }
+}
+
+// out[r, k] = mu + sigma * (cb[c] - codesum/gs); one thread per chunk of 8 codes.
+template <int BITS, typename OUT>
+__global__ void dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ mu,
+                               const float* __restrict__ sigma, const float* __restrict__ codesum,
+                               const float* __restrict__ codebook, long long rows, int K, int gs,
+                               OUT* __restrict__ out) {
+  __shared__ float s_cb[16];
+  if (threadIdx.x < 16) s_cb[threadIdx.x] = (threadIdx.x < (1 << BITS)) ? codebook[threadIdx.x] : 0.0f;
+  __syncthreads();
+  const int chunks = K / 8;
+  const int G = K / gs;
+  const long long pc = static_cast<long long>(K) * BITS / 8;
+  const long long total = rows * chunks;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / chunks;
+    const int ch = static_cast<int>(i - r * chunks);
+    const int g = (ch * 8) / gs;
+    const uint32_t w = load_codes8<BITS>(packed + r * pc, ch);
+    const float m = mu[r * G + g], s = sigma[r * G + g];
+    const float vm = __fdiv_rn(codesum[r * G + g], static_cast<float>(gs));
+    OUT* o = out + r * K + ch * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float v = __fadd_rn(m, __fmul_rn(s, __fsub_rn(s_cb[(w >> (4 * j)) & 15u], vm)));
+      store_from_f32<OUT>(o + j, v);
+    }
+  }
+}
+
+}  // namespace arcq

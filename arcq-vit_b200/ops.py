@@ -1,0 +1,171 @@
+"""Operator layer over the C ABI: torch tensors in, torch tensors out.
+
+Mirrors the operator set of the reference's CUDA extension
+(methods/fair_qat_framework/fair_qat/arcq_infer_cuda/arcq_infer_bind.cpp:57-66):
+``quantize_activation``, ``quantize_activation_dequant``, ``arcq_linear_forward``,
+``pack_codes``, ``unpack_codes`` / ``unpack_codes_u8``.  torch is used only for device
+memory and the current stream; all arithmetic happens in ``libarcq_b200.so``.
+Bad arguments raise ``RuntimeError`` like the reference's ``TORCH_CHECK``s.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _cabi
+
+_DT = {torch.float32: _cabi.DT_F32, torch.float16: _cabi.DT_F16, torch.bfloat16: _cabi.DT_BF16}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed ({rc}): {_cabi.last_error()}")
+
+
+def _dev(t: torch.Tensor, name: str, dtype=None) -> torch.Tensor:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.contiguous()
+
+
+def packed_cols(length: int, bits: int) -> int:
+    return (length * bits + 7) // 8
+
+
+def device_status() -> int:
+    """0, or the code a kernel left when one of its bounded waits ran out (synchronises)."""
+    return int(_cabi.load().arcq_device_status())
+
+
+def quantize_activation(x: torch.Tensor, thresholds: torch.Tensor, codebook: torch.Tensor, bits: int,
+                        group_size: int, want_code_sum: bool = True):
+    """[M,K] float -> (packed uint8 [M, K*bits/8], center, scale, code_sum fp32 [M, K/group_size]).
+
+    Same contract as the reference's ``quantize_activation`` (arcq_activation_kernel.cu:188-237),
+    except that fp16 / bf16 inputs are read as they are instead of being copied to fp32 first.
+    """
+    lib = _cabi.load()
+    if x.dim() != 2:
+        raise RuntimeError(f"x must be 2-D, got shape {tuple(x.shape)}")
+    if x.dtype not in _DT:
+        raise RuntimeError(f"x must be float32, float16 or bfloat16, got {x.dtype}")
+    x = _dev(x, "x")
+    th = _dev(thresholds, "thresholds", torch.float32)
+    cb = _dev(codebook, "codebook", torch.float32)
+    if cb.numel() != 2 ** bits or th.numel() != 2 ** bits - 1:
+        raise RuntimeError(f"codebook/thresholds must have {2 ** bits}/{2 ** bits - 1} entries")
+    M, K = x.shape
+    if group_size <= 0 or K % group_size != 0:
+        raise RuntimeError(f"K={K} is not a multiple of group_size={group_size}")
+    G = K // group_size
+    packed = torch.empty((M, packed_cols(K, bits)), dtype=torch.uint8, device=x.device)
+    mu = torch.empty((M, G), dtype=torch.float32, device=x.device)
+    sg = torch.empty_like(mu)
+    cs = torch.empty_like(mu) if want_code_sum else None
+    rc = lib.arcq_act_quant(x.data_ptr(), _DT[x.dtype], M, K, th.data_ptr(), cb.data_ptr(), bits, group_size,
+                            packed.data_ptr(), mu.data_ptr(), sg.data_ptr(), cs.data_ptr() if cs is not None else None,
+                            None, 0, _stream())
+    _check(rc, "arcq_act_quant")
+    return packed, mu, sg, cs
+
+
+def quantize_activation_dequant(x: torch.Tensor, thresholds: torch.Tensor, codebook: torch.Tensor, bits: int,
+                                group_size: int, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """[M,K] float -> reconstruction [M,K] (reference: arcq_activation_kernel.cu:286-326)."""
+    lib = _cabi.load()
+    if x.dim() != 2 or x.dtype not in _DT or out_dtype not in _DT:
+        raise RuntimeError("x must be a 2-D float tensor and out_dtype a float dtype")
+    x = _dev(x, "x")
+    th = _dev(thresholds, "thresholds", torch.float32)
+    cb = _dev(codebook, "codebook", torch.float32)
+    M, K = x.shape
+    out = torch.empty((M, K), dtype=out_dtype, device=x.device)
+    rc = lib.arcq_act_quant(x.data_ptr(), _DT[x.dtype], M, K, th.data_ptr(), cb.data_ptr(), bits, group_size,
+                            None, None, None, None, out.data_ptr(), _DT[out_dtype], _stream())
+    _check(rc, "arcq_act_quant")
+    return out
+
+
+def arcq_linear_forward(packed_x, x_center, x_scale, x_code_sum, packed_w, w_center, w_scale, w_code_sum,
+                        act_codebook, w_codebook, bias, bits: int, group_size: int, in_features: int,
+                        out_features: int, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Packed linear (reference: arcq_linear_forward, arcq_linear_kernel.cu:206-278).
+
+    The reference takes ``product_table = outer(act_codebook, w_codebook)``; the two codebooks
+    are passed here instead.  Returns [M, out_features] in ``out_dtype`` (fp32 or fp16).
+    """
+    lib = _cabi.load()
+    packed_x = _dev(packed_x, "packed_x", torch.uint8)
+    packed_w = _dev(packed_w, "packed_w", torch.uint8)
+    f = [_dev(t, n, torch.float32) for t, n in (
+        (x_center, "x_center"), (x_scale, "x_scale"), (x_code_sum, "x_code_sum"), (w_center, "w_center"),
+        (w_scale, "w_scale"), (w_code_sum, "w_code_sum"), (act_codebook, "act_codebook"), (w_codebook, "w_codebook"))]
+    if out_dtype not in (torch.float32, torch.float16):
+        raise RuntimeError("out_dtype must be float32 or float16")
+    M = packed_x.shape[0]
+    pc = packed_cols(in_features, bits)
+    if packed_x.shape[1] != pc or tuple(packed_w.shape) != (out_features, pc):
+        raise RuntimeError(f"packed shapes {tuple(packed_x.shape)}/{tuple(packed_w.shape)} do not match "
+                           f"K={in_features} N={out_features} bits={bits}")
+    b = None
+    if bias is not None and bias.numel() > 0:
+        b = _dev(bias, "bias", torch.float32)
+        if b.numel() != out_features:
+            raise RuntimeError("bias must have out_features entries")
+    y = torch.empty((M, out_features), dtype=out_dtype, device=packed_x.device)
+    rc = lib.arcq_packed_gemm(packed_x.data_ptr(), f[0].data_ptr(), f[1].data_ptr(), f[2].data_ptr(),
+                              packed_w.data_ptr(), f[3].data_ptr(), f[4].data_ptr(), f[5].data_ptr(),
+                              f[6].data_ptr(), f[7].data_ptr(), b.data_ptr() if b is not None else None,
+                              bits, group_size, M, out_features, in_features, y.data_ptr(), _DT[out_dtype], _stream())
+    _check(rc, "arcq_packed_gemm")
+    return y
+
+
+def unpack_codes_u8(packed: torch.Tensor, bits: int, length: int) -> torch.Tensor:
+    """uint8 [R, ceil(length*bits/8)] -> uint8 [R, length] (reference: arcq_pack_kernel.cu:136-157)."""
+    lib = _cabi.load()
+    packed = _dev(packed, "packed", torch.uint8)
+    if packed.dim() != 2 or packed.shape[1] != packed_cols(length, bits):
+        raise RuntimeError(f"packed shape {tuple(packed.shape)} does not match length={length} bits={bits}")
+    out = torch.empty((packed.shape[0], length), dtype=torch.uint8, device=packed.device)
+    _check(lib.arcq_unpack_codes(packed.data_ptr(), packed.shape[0], length, bits, out.data_ptr(), _stream()),
+           "arcq_unpack_codes")
+    return out
+
+
+def unpack_codes(packed: torch.Tensor, bits: int, length: int) -> torch.Tensor:
+    """As ``unpack_codes_u8`` but int64, the reference's ``unpack_codes`` (arcq_pack_kernel.cu:113-134)."""
+    return unpack_codes_u8(packed, bits, length).to(torch.int64)
+
+
+def pack_codes(codes: torch.Tensor, bits: int) -> torch.Tensor:
+    """integer codes [R, length] -> uint8 [R, ceil(length*bits/8)] (reference: arcq_pack_kernel.cu:92-111)."""
+    lib = _cabi.load()
+    if not codes.is_cuda or codes.dim() != 2:
+        raise RuntimeError("codes must be a 2-D CUDA tensor")
+    c8 = codes.to(torch.uint8).contiguous()
+    R, length = c8.shape
+    out = torch.empty((R, packed_cols(length, bits)), dtype=torch.uint8, device=codes.device)
+    _check(lib.arcq_pack_codes(c8.data_ptr(), R, length, bits, out.data_ptr(), _stream()), "arcq_pack_codes")
+    return out
+
+
+def dequant(packed, center, scale, code_sum, codebook, bits: int, group_size: int,
+            out_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """Packed codes + statistics -> [R, K] matrix; what the reference's ``unpack_weight_triton``
+    (arcq_packed_triton.py:77-120) writes.  For tests and debugging only."""
+    lib = _cabi.load()
+    packed = _dev(packed, "packed", torch.uint8)
+    center, scale, code_sum, codebook = (_dev(t, "stats", torch.float32) for t in (center, scale, code_sum, codebook))
+    R, G = center.shape
+    K = G * group_size
+    out = torch.empty((R, K), dtype=out_dtype, device=packed.device)
+    _check(lib.arcq_dequant(packed.data_ptr(), center.data_ptr(), scale.data_ptr(), code_sum.data_ptr(),
+                            codebook.data_ptr(), bits, group_size, R, K, out.data_ptr(), _DT[out_dtype], _stream()),
+           "arcq_dequant")
+    return out

@@ -1,0 +1,334 @@
+"""Benchmark of the ARCQ packed inference path: whole-model DeiT forward, images/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--model deit_small] [--bits 4] [--batch 64]
+
+A step is one forward of a batch of synthetic 224x224 images through the packed model (48 packed
+linears = 48 activation-quantise launches + 48 fused packed-GEMM launches, plus the floating-point
+glue).  With N > 1 (one process per GPU under torchrun) every rank runs its own batch (weak scaling)
+and the logits are all-gathered over NCCL each step.  Rank 0 prints one JSON line.
+
+`value` is timed with the batch already in HBM (CUDA-graph replay); `e2e` copies each step's batch
+from pinned host memory and reads the logits back inside the timed region.  `roofline` is the fused
+packed GEMM (the dominant kernel) timed alone on the model's four layer shapes; `cpu_baseline` is
+the CPU oracle port of the reference's fake-quant path on the host cores.  `--impl reference`
+prints the same line for that CPU path alone.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+import __graft_entry__ as entry  # noqa: E402
+
+METRIC = "images_per_sec"
+TOKENS = 197
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--model", default="deit_small", choices=["deit_tiny", "deit_small", "deit_base"])
+    ap.add_argument("--bits", type=int, default=4, choices=[3, 4])
+    ap.add_argument("--batch", type=int, default=64, help="images per GPU per step")
+    ap.add_argument("--no-graph", action="store_true", help="eager launches instead of CUDA-graph replay")
+    ap.add_argument("--cpu-sample", type=int, default=8, help="images in the CPU-baseline sample batch")
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def workload_name(a) -> str:
+    return f"{a.model} W{a.bits}A{a.bits} packed forward, batch {a.batch}/GPU, 224x224 synthetic images"
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=float(d["hbm_gbs"]), tflops=float(d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, source="fallback")
+
+
+# ---------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()          # the exact process started above
+        self.proc.wait(timeout=5)
+        sm, smax, reasons = [], [], set()
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(smax) if smax else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+# ---------------------------------------------------------------------------------- CPU path
+def cpu_reference_run(a, steps: int, warmup: int, sample_images: int):
+    """The reference's CPU fake-quant forward, as restated by the oracle, on all host cores."""
+    from oracle.fakequant_vit import OracleViT
+    O = entry.import_oracle()
+    pkg = entry.import_package()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    O.set_threads(cores)
+    m = pkg.create_vit(a.model, seed=0)
+    dim, heads, depth = pkg.DEIT_CONFIGS[a.model]
+    o = OracleViT(m.state_dict(), dim, heads, depth, a.bits, cache_weights=False)
+    imgs = torch.randn(sample_images, 3, 224, 224, generator=torch.Generator().manual_seed(1))
+    o(imgs)                                   # calibrating forward (codebook compile), not timed
+    for _ in range(max(0, warmup - 1)):
+        o(imgs)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        o(imgs)
+    dt = time.perf_counter() - t0
+    return dict(value=sample_images * steps / dt, ms_per_step=1e3 * dt / steps, cores=cores,
+                sample=f"{steps} forwards of a {sample_images}-image batch of the same model after {warmup} warm-up")
+
+
+def run_reference_arm(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = min(a.steps, 3), max(1, min(a.warmup, 2))
+    r = cpu_reference_run(a, steps, warmup, a.cpu_sample)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "images/s", "n_gpus": a.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(a), "note": "CPU fake-quant path of the reference (oracle port), "
+                   f"{a.cpu_sample}-image batches on host cores"},
+        "cpu_baseline": {"value": r["value"], "unit": "images/s", "cores": r["cores"], "kind": "port",
+                         "sample": r["sample"]},
+        "e2e": {"value": r["value"], "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------- GPU path
+def layer_shapes(pkg, model: str):
+    dim = pkg.DEIT_CONFIGS[model][0]
+    return [("qkv", dim, 3 * dim), ("proj", dim, dim), ("fc1", dim, 4 * dim), ("fc2", 4 * dim, dim)]
+
+
+def kernel_rooflines(pkg, a, dev, pk):
+    """Time the two kernels alone on the model's layer shapes (CUDA events on the launch stream, rotating
+    buffers so operands and results come from / go to HBM rather than L2)."""
+    M, bits = a.batch * TOKENS, a.bits
+    cb = torch.linspace(-2.6, 2.6, 2 ** bits, device=dev)
+    th = (cb[:-1] + cb[1:]) / 2
+    gen = torch.Generator().manual_seed(7)
+    reps, rot = 20, 4
+    out = {}
+    tot_flop = tot_ms = tot_bytes = aq_bytes = aq_ms = 0.0
+    per_layer = []
+    for name, K, N in layer_shapes(pkg, a.model):
+        xs = [torch.randn(M, K, generator=gen).half().to(dev) for _ in range(rot)]
+        w = (torch.randn(N, K, generator=gen) * 0.02).to(dev)
+        bias = torch.zeros(N, device=dev)
+        pw, mw, sw, cw = pkg.ops.quantize_activation(w, th, cb, bits, 64)
+        qa = [pkg.ops.quantize_activation(x, th, cb, bits, 64) for x in xs]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(3):
+            pkg.ops.arcq_linear_forward(*qa[i % rot], pw, mw, sw, cw, cb, cb, bias, bits, 64, K, N, torch.float16)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(reps):
+            pkg.ops.arcq_linear_forward(*qa[i % rot], pw, mw, sw, cw, cb, cb, bias, bits, 64, K, N, torch.float16)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        G = K // 64
+        nbytes = M * K * bits // 8 + M * G * 12 + N * K * bits // 8 + N * G * 12 + 2 * (2 ** bits) * 4 + N * 4 + M * N * 2
+        flop = 2.0 * M * N * K
+        per_layer.append(dict(layer=name, M=M, K=K, N=N, ms=ms, tflops=flop / ms / 1e9, gbs=nbytes / ms / 1e6))
+        tot_flop, tot_ms, tot_bytes = tot_flop + flop, tot_ms + ms, tot_bytes + nbytes
+        # activation quantizer on the same input
+        for i in range(3):
+            pkg.ops.quantize_activation(xs[i % rot], th, cb, bits, 64)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(reps):
+            pkg.ops.quantize_activation(xs[i % rot], th, cb, bits, 64)
+        e1.record()
+        torch.cuda.synchronize()
+        qms = e0.elapsed_time(e1) / reps
+        aq_bytes += M * K * 2 + M * K * bits // 8 + M * G * 12
+        aq_ms += qms
+        per_layer[-1].update(act_quant_ms=qms, act_quant_gbs=(M * K * 2 + M * K * bits // 8 + M * G * 12) / qms / 1e6)
+    achieved = tot_flop / tot_ms / 1e9
+    out["roofline"] = {"kernel": "packed_gemm_kernel", "bound": "tensor", "achieved": achieved, "peak": pk["tflops"],
+                       "unit": "TFLOP/s", "frac": achieved / pk["tflops"], "traffic": None,
+                       "peak_source": pk["source"] + " cuBLAS bf16 burst",
+                       "algorithmic_bytes_per_launch_avg": tot_bytes / 4, "ms_per_launch_avg": tot_ms / 4,
+                       "per_layer": per_layer}
+    aq = aq_bytes / aq_ms / 1e6
+    out["roofline_act_quant"] = {"kernel": "act_quant_kernel", "bound": "hbm", "achieved": aq, "peak": pk["hbm_gbs"],
+                                 "unit": "GB/s", "frac": aq / pk["hbm_gbs"], "traffic": None,
+                                 "peak_source": pk["source"] + " copy"}
+    return out
+
+
+def run_gpu_arm(a):
+    pkg = entry.import_package()
+    pkg._cabi.load()                      # raises if the CUDA library is not built: there is no fallback
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (use --impl reference for the CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B = a.batch
+    gen = torch.Generator().manual_seed(100 + rank)
+    n_rot = 4
+    host_batches = [torch.randn(B, 3, 224, 224, generator=gen).half().pin_memory() for _ in range(n_rot)]
+    dev_batches = [h.to(dev) for h in host_batches]
+
+    model = pkg.create_vit(a.model, seed=0).half().to(dev)
+    with torch.no_grad():
+        model = pkg.quantise_model(model, dev_batches[0], a.bits)      # codebooks calibrated on the first batch
+    n_lin = pkg.count_packed_linear(model)
+    runner = model if a.no_graph else pkg.GraphedModel(model, dev_batches[0])
+    global_batch = B * world
+    gathered = None
+
+    def step(x):
+        nonlocal gathered
+        with torch.no_grad():
+            y = runner(x)
+        if world > 1:
+            gathered = pkg.sharding.gather_logits(y, global_batch)
+        return y
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- device-resident timing
+    for i in range(max(3, a.warmup)):
+        step(dev_batches[i % n_rot])
+    sync_all()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.steps):
+        step(dev_batches[i % n_rot])
+    e1.record()
+    sync_all()
+    ms = e0.elapsed_time(e1)
+    # ---- end to end: pinned host batch in, logits out, every step
+    stage = torch.empty_like(dev_batches[0])
+    host_logits = torch.empty(B, 1000, dtype=torch.float16).pin_memory()
+    for i in range(3):
+        stage.copy_(host_batches[i % n_rot], non_blocking=True)
+        host_logits.copy_(step(stage), non_blocking=True)
+    sync_all()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for i in range(a.steps):
+        stage.copy_(host_batches[i % n_rot], non_blocking=True)
+        host_logits.copy_(step(stage), non_blocking=True)
+        torch.cuda.current_stream().synchronize()       # the caller reads the logits before the next batch
+    f1.record()
+    sync_all()
+    ms_e2e = f0.elapsed_time(f1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+    status = pkg.ops.device_status()
+
+    if rank == 0:
+        pk = peaks()
+        extra = kernel_rooflines(pkg, a, dev, pk)
+        cpu = None
+        if world == 1 and not a.skip_cpu_baseline:
+            r = cpu_reference_run(a, 2, 1, a.cpu_sample)
+            cpu = {"value": r["value"], "unit": "images/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]}
+        act_bytes = B * TOKENS * pkg.DEIT_CONFIGS[a.model][0] * 2
+        line = {
+            "metric": METRIC, "value": global_batch * a.steps / (ms / 1e3), "unit": "images/s", "n_gpus": world,
+            "steps": a.steps, "warmup": max(3, a.warmup), "ms_per_step": ms / a.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": workload_name(a), "global_batch": global_batch, "packed_linears": n_lin,
+                       "cuda_graph": not a.no_graph, "parallelism": f"batch-sharded x{world}, logits all-gather",
+                       "l2": f"{n_rot} rotating input batches; one forward streams > 1 GB of activations "
+                             f"({act_bytes / 1e6:.0f} MB per [M,dim] tensor) through the 126 MB L2",
+                       "weights": "random init, seed 0; codebooks fitted on the first batch, then frozen"},
+            "e2e": {"value": global_batch * a.steps / (ms_e2e / 1e3), "unit": "images/s",
+                    "h2d_bytes_per_step": host_batches[0].numel() * 2, "d2h_bytes_per_step": host_logits.numel() * 2,
+                    "ms_per_step": ms_e2e / a.steps},
+            "gpu_launches": 2 * n_lin * a.steps,
+            "clocks": clocks, "device_status": status,
+        }
+        line.update(extra)
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference_arm(a)
+    else:
+        run_gpu_arm(a)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,132 @@
+/*
+ * arcq_b200 -- C ABI of the B200 (sm_100a) back end for the ARCQ packed inference path.
+ *
+ * Plain C entry points: raw device pointers, sizes, an opaque CUDA stream.  No
+ * allocation happens inside unless an entry point says so; every call is
+ * enqueued on the given stream and returns without synchronising.  Return value
+ * 0 = success, negative = the call was rejected before any launch (see the
+ * ARCQ_E_* codes; arcq_last_error_string() gives the reason for the calling
+ * thread).
+ *
+ * Each declaration names the interface of the reference project it stands in
+ * for.  Paths are inside the reference project; FQ = methods/fair_qat_framework,
+ * EXT = FQ/fair_qat/arcq_infer_cuda.
+ *
+ * Data layout shared by all entry points (row-major, contiguous):
+ *   packed codes   uint8 [rows, ceil(len*bits/8)]  code j of a row in bits [j*bits,(j+1)*bits) of
+ *                  a little-endian bit stream (FQ/fair_qat/arcq_packed_py.py:8-78)
+ *   per-group stats fp32 [rows, len/group_size]   mean, scale, sum of code values
+ *   codebook       fp32 [2^bits] ascending;  thresholds fp32 [2^bits-1] = midpoints
+ */
+#ifndef ARCQ_B200_H_
+#define ARCQ_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ARCQ_B200_VERSION 100
+
+/* element types of x / y arguments */
+#define ARCQ_DT_F32 0
+#define ARCQ_DT_F16 1
+#define ARCQ_DT_BF16 2
+
+/* error codes */
+#define ARCQ_OK 0
+#define ARCQ_E_BAD_ARG (-1)      /* null pointer, bad dtype, bits not in {2,3,4}, ... */
+#define ARCQ_E_BAD_SHAPE (-2)    /* K not a multiple of the group size, N not a multiple of 8, ... */
+#define ARCQ_E_UNSUPPORTED (-3)  /* valid in the reference but not built here (group size != 64) */
+#define ARCQ_E_ALIGN (-4)        /* pointer not aligned as the kernel needs */
+#define ARCQ_E_CUDA (-5)         /* the CUDA runtime refused the launch */
+#define ARCQ_E_TOO_LARGE (-6)    /* beyond a fixed capacity of the entry point */
+
+/* Library version (ARCQ_B200_VERSION of the build).  No reference counterpart. */
+int arcq_version(void);
+
+/* Reason for the last non-zero return on the calling thread ("" if none).
+ * Stands in for the TORCH_CHECK messages of EXT/arcq_activation_kernel.cu:194-202. */
+const char* arcq_last_error_string(void);
+
+/*
+ * Device-side status word of the current device: 0, or a non-zero code left by a
+ * kernel whose bounded wait ran out (the kernel then returned early instead of
+ * hanging).  Reading it synchronises the device and clears the word.
+ * No reference counterpart (the reference kernels have no waits).
+ */
+int arcq_device_status(void);
+
+/*
+ * Activation quantizer: per row and per group of `group_size` consecutive
+ * elements computes mean, scale = sqrt(mean(r^2)+1e-6), the code of every
+ * element (number of thresholds below (x-mean)/scale) and the sum of code
+ * values; writes packed codes and the three statistics.
+ * Replaces quantize_activation_cuda, EXT/arcq_activation_kernel.cu:188-237
+ * (kernel :24-77), and the quantising half of dequant_activation_triton,
+ * FQ/fair_qat/arcq_packed_triton.py:181-215.  Arithmetic is fp32 with IEEE
+ * division and square root and a fixed summation order, so codes equal the
+ * reference CPU quantizer's (FQ/quant/dcarcq.py:531-556) bit for bit.
+ *   x            [M,K] of x_dtype;  K % group_size == 0;  group_size must be 64
+ *   packed_out   uint8 [M, K*bits/8]      (may be NULL when xhat_out is given)
+ *   mu_out, sigma_out   fp32 [M, K/64]    (may be NULL together with packed_out)
+ *   codesum_out  fp32 [M, K/64] or NULL
+ *   xhat_out     optional [M,K] of xhat_dtype: the reconstruction
+ *                mean + scale*(cb[c] - codesum/64), the output of
+ *                quantize_activation_dequant_cuda, EXT/arcq_activation_kernel.cu:286-326
+ */
+int arcq_act_quant(const void* x, int x_dtype, int64_t M, int64_t K,
+                   const float* thresholds, const float* codebook, int bits, int group_size,
+                   uint8_t* packed_out, float* mu_out, float* sigma_out, float* codesum_out,
+                   void* xhat_out, int xhat_dtype, void* stream);
+
+/*
+ * Packed linear:  y[m,n] = bias[n] + sum_k A^[m,k] * W^[n,k]  with both operands
+ * reconstructed from packed codes, A^ = mu_a + sigma_a*(cbA[ca] - Sa/gs) and
+ * likewise W^, contracted on the tensor cores in fp16 with fp32 accumulation.
+ * Replaces arcq_linear_forward_cuda, EXT/arcq_linear_kernel.cu:206-278 (kernel
+ * :22-78), and steps 3-5 of ARCQPackedLinearOnTheFly.forward,
+ * FQ/fair_qat/arcq_packed_on_the_fly.py:147-161 (Triton weight unpack + F.linear).
+ * The reference passes product_table = outer(act_cb, w_cb); this entry point takes
+ * the two codebooks instead.
+ *   packed_x [M, K*bits/8], mu_a/sigma_a/codesum_a fp32 [M, K/gs]
+ *   packed_w [N, K*bits/8], mu_w/sigma_w/codesum_w fp32 [N, K/gs]
+ *   bias fp32 [N] or NULL;  y [M,N] of y_dtype (ARCQ_DT_F16 or ARCQ_DT_F32)
+ *   group_size must be 64; N % 8 == 0.
+ */
+int arcq_packed_gemm(const uint8_t* packed_x, const float* mu_a, const float* sigma_a,
+                     const float* codesum_a, const uint8_t* packed_w, const float* mu_w,
+                     const float* sigma_w, const float* codesum_w, const float* act_codebook,
+                     const float* w_codebook, const float* bias, int bits, int group_size,
+                     int64_t M, int64_t N, int64_t K, void* y, int y_dtype, void* stream);
+
+/*
+ * Unpack codes to one byte per code.  Replaces unpack_codes_u8_cuda,
+ * EXT/arcq_pack_kernel.cu:136-157 (kernel :74-90); the int64 variant
+ * unpack_codes_cuda (:113-134) is this plus a widening on the host side.
+ */
+int arcq_unpack_codes(const uint8_t* packed, int64_t rows, int64_t length, int bits,
+                      uint8_t* codes_out, void* stream);
+
+/*
+ * Pack one-byte codes into the bit stream.  Replaces pack_codes_cuda,
+ * EXT/arcq_pack_kernel.cu:92-111 (kernel :38-54), which takes int64 codes.
+ */
+int arcq_pack_codes(const uint8_t* codes, int64_t rows, int64_t length, int bits,
+                    uint8_t* packed_out, void* stream);
+
+/*
+ * Reconstruct an fp16/fp32 matrix from packed codes and statistics:
+ * out = mu + sigma*(cb[c] - codesum/gs).  Replaces unpack_weight_triton,
+ * FQ/fair_qat/arcq_packed_triton.py:77-120 (kernel :11-74); kept for tests and
+ * debugging -- the linear above never materialises this matrix.
+ */
+int arcq_dequant(const uint8_t* packed, const float* mu, const float* sigma, const float* codesum,
+                 const float* codebook, int bits, int group_size, int64_t rows, int64_t K,
+                 void* out, int out_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ARCQ_B200_H_ */
