@@ -12,6 +12,8 @@
 #include "act_quant.cuh"
 #include "codes.cuh"
 #include "packed_gemm.cuh"
+#include "gemm_ws.cuh"
+#include <cudaTypedefs.h>
 
 namespace {
 
@@ -115,6 +117,83 @@ int choose_bn(long long M, long long N) {
   return static_cast<int>(r < 256 ? r : 256);
 }
 
+
+// ---- tensor maps (driver entry point fetched through the runtime, so libcuda is not linked) ----
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of `elem_bytes`-byte elements, box [box_cols x box_rows].
+bool make_tensor_map_2d(CUtensorMap* tm, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows,
+                        uint64_t cols, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swz) {
+  PFN_cuTensorMapEncodeTiled_v12000 enc = tensor_map_encoder();
+  if (enc == nullptr) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * static_cast<uint64_t>(elem_bytes)};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct WsConfig {
+  int bn, ws, sa, nbb, stationary, grid;
+  size_t smem;
+};
+
+// Shared memory one CTA may ask for on B200 (227 KB) minus the 1 KB alignment slack.
+constexpr size_t kSmemBudget = 232448 - 1024;
+
+// Pick slab width, ring depths and grid for the warp-specialised GEMM; false if the shape is not
+// one it handles (the caller then reports ARCQ_E_UNSUPPORTED).
+bool choose_ws_config(long long M, long long N, long long K, int bits, WsConfig* c) {
+  const int G = static_cast<int>(K / 64);
+  const long long tiles_m = (M + arcq::kTileM - 1) / arcq::kTileM;
+  const int sms = sm_count();
+  static const int cand[] = {192, 256, 128, 96, 64, 48, 32, 16};
+  int best_bn = 0;
+  long long best_ctas = -1;
+  for (int bn : cand) {
+    if (N % bn != 0) continue;
+    const long long slabs = N / bn;
+    if (slabs > sms) continue;
+    const long long per = sms / slabs;
+    const long long ctas = slabs * (tiles_m < per ? tiles_m : per);
+    if (ctas * 4 >= 3LL * sms) { best_bn = bn; best_ctas = ctas; break; }  // first (widest) that fills 3/4 of the SMs
+    if (ctas > best_ctas) { best_ctas = ctas; best_bn = bn; }
+  }
+  if (best_bn == 0) return false;
+  c->bn = best_bn;
+  const long long slabs = N / best_bn;
+  const long long per = sms / slabs;
+  c->grid = static_cast<int>(slabs * (tiles_m < per ? tiles_m : per));
+  // stationary if all G sub-tiles plus two A stages fit
+  for (int stationary = 1; stationary >= 0; --stationary) {
+    const int ws = stationary ? G : (G < 3 ? G : 3);
+    if (ws > 16) continue;
+    for (int sa = 6; sa >= 2; --sa) {
+      const size_t need = arcq::ws_smem_layout(best_bn, ws, sa, bits).total;
+      if (need <= kSmemBudget) {
+        c->ws = ws; c->sa = sa; c->stationary = stationary;
+        c->nbb = stationary ? 1 : 2;
+        c->smem = need + 1024;
+        return true;
+      }
+    }
+  }
+  return false;
+}
+
 }  // namespace
 
 extern "C" {
@@ -215,6 +294,65 @@ int arcq_packed_gemm(const uint8_t* packed_x, const float* mu_a, const float* si
   else ARCQ_LAUNCH_GEMM(2);
 #undef ARCQ_LAUNCH_GEMM
   if (e != cudaSuccess) return cuda_fail(e, "packed_gemm launch");
+  return ARCQ_OK;
+}
+
+
+int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const float* mu_w, const float* sigma_w,
+                            const float* codesum_w, const float* w_codebook, const float* bias, int bits,
+                            int group_size, int64_t M, int64_t N, int64_t K, void* y, int y_dtype, void* stream) {
+  if (!xhat || !packed_w || !mu_w || !sigma_w || !codesum_w || !w_codebook || !y)
+    return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
+  if (y_dtype != ARCQ_DT_F16 && y_dtype != ARCQ_DT_F32) return fail(ARCQ_E_BAD_ARG, "y_dtype must be f16 or f32");
+  if (M < 0 || N <= 0 || K <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape M=%lld N=%lld K=%lld", (long long)M,
+                                              (long long)N, (long long)K);
+  if (group_size <= 0 || K % group_size != 0)
+    return fail(ARCQ_E_BAD_SHAPE, "K=%lld is not a multiple of group_size=%d", (long long)K, group_size);
+  if (group_size != 64) return fail(ARCQ_E_UNSUPPORTED, "group_size %d: only 64 is built", group_size);
+  if (N % 16 != 0) return fail(ARCQ_E_UNSUPPORTED, "N=%lld: this entry point needs N %% 16 == 0", (long long)N);
+  if ((K * bits / 8) % 16 != 0)
+    return fail(ARCQ_E_UNSUPPORTED, "packed row of %lld bytes is not a multiple of 16 (TMA stride rule)",
+                (long long)(K * bits / 8));
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > (1 << 20)) return fail(ARCQ_E_TOO_LARGE, "shape too large");
+  if (!aligned(xhat, 16) || !aligned(packed_w, 16) || !aligned(y, 16))
+    return fail(ARCQ_E_ALIGN, "xhat, packed_w and y must be 16-byte aligned");
+  if (M == 0) return ARCQ_OK;
+  WsConfig cfg;
+  if (!choose_ws_config(M, N, K, bits, &cfg)) return fail(ARCQ_E_UNSUPPORTED, "no tile configuration for this shape");
+
+  CUtensorMap tm_a, tm_w;
+  if (!make_tensor_map_2d(&tm_a, xhat, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, static_cast<uint64_t>(M),
+                          static_cast<uint64_t>(K), 64, arcq::kTileM, CU_TENSOR_MAP_SWIZZLE_128B))
+    return fail(ARCQ_E_CUDA, "cuTensorMapEncodeTiled failed for the activation matrix");
+  if (!make_tensor_map_2d(&tm_w, packed_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, static_cast<uint64_t>(N),
+                          static_cast<uint64_t>(K * bits / 8), arcq::raw_row_bytes(bits), cfg.bn,
+                          CU_TENSOR_MAP_SWIZZLE_NONE))
+    return fail(ARCQ_E_CUDA, "cuTensorMapEncodeTiled failed for the packed weight");
+
+  arcq::WsParams p;
+  p.mu_w = mu_w; p.sg_w = sigma_w; p.cs_w = codesum_w; p.cb_w = w_codebook; p.bias = bias; p.y = y;
+  p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K); p.G = static_cast<int>(K / 64);
+  p.bn = cfg.bn; p.ws = cfg.ws; p.sa = cfg.sa; p.nbb = cfg.nbb; p.stationary = cfg.stationary;
+  p.y_f32 = (y_dtype == ARCQ_DT_F32) ? 1 : 0;
+  p.status = status_ptr();
+  if (p.status == nullptr) return fail(ARCQ_E_CUDA, "device status word not reachable");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaSuccess;
+#define ARCQ_LAUNCH_WS(B)                                                                                          \
+  do {                                                                                                             \
+    e = cudaFuncSetAttribute(arcq::packed_weight_gemm_ws_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                             static_cast<int>(cfg.smem));                                                          \
+    if (e == cudaSuccess) {                                                                                        \
+      arcq::packed_weight_gemm_ws_kernel<B><<<cfg.grid, arcq::kWsThreads, cfg.smem, st>>>(tm_a, tm_w, p);          \
+      e = cudaGetLastError();                                                                                      \
+    }                                                                                                              \
+  } while (0)
+  if (bits == 4) ARCQ_LAUNCH_WS(4);
+  else if (bits == 3) ARCQ_LAUNCH_WS(3);
+  else ARCQ_LAUNCH_WS(2);
+#undef ARCQ_LAUNCH_WS
+  if (e != cudaSuccess) return cuda_fail(e, "packed_weight_gemm launch");
   return ARCQ_OK;
 }
 

@@ -67,6 +67,8 @@ def quantize_activation(x: torch.Tensor, thresholds: torch.Tensor, codebook: tor
     mu = torch.empty((M, G), dtype=torch.float32, device=x.device)
     sg = torch.empty_like(mu)
     cs = torch.empty_like(mu) if want_code_sum else None
+    if M == 0:
+        return packed, mu, sg, cs
     rc = lib.arcq_act_quant(x.data_ptr(), _DT[x.dtype], M, K, th.data_ptr(), cb.data_ptr(), bits, group_size,
                             packed.data_ptr(), mu.data_ptr(), sg.data_ptr(), cs.data_ptr() if cs is not None else None,
                             None, 0, _stream())
@@ -85,6 +87,8 @@ def quantize_activation_dequant(x: torch.Tensor, thresholds: torch.Tensor, codeb
     cb = _dev(codebook, "codebook", torch.float32)
     M, K = x.shape
     out = torch.empty((M, K), dtype=out_dtype, device=x.device)
+    if M == 0:
+        return out
     rc = lib.arcq_act_quant(x.data_ptr(), _DT[x.dtype], M, K, th.data_ptr(), cb.data_ptr(), bits, group_size,
                             None, None, None, None, out.data_ptr(), _DT[out_dtype], _stream())
     _check(rc, "arcq_act_quant")
@@ -118,11 +122,52 @@ def arcq_linear_forward(packed_x, x_center, x_scale, x_code_sum, packed_w, w_cen
         if b.numel() != out_features:
             raise RuntimeError("bias must have out_features entries")
     y = torch.empty((M, out_features), dtype=out_dtype, device=packed_x.device)
+    if M == 0:
+        return y
     rc = lib.arcq_packed_gemm(packed_x.data_ptr(), f[0].data_ptr(), f[1].data_ptr(), f[2].data_ptr(),
                               packed_w.data_ptr(), f[3].data_ptr(), f[4].data_ptr(), f[5].data_ptr(),
                               f[6].data_ptr(), f[7].data_ptr(), b.data_ptr() if b is not None else None,
                               bits, group_size, M, out_features, in_features, y.data_ptr(), _DT[out_dtype], _stream())
     _check(rc, "arcq_packed_gemm")
+    return y
+
+
+def packed_weight_gemm_supported(in_features: int, out_features: int, bits: int, group_size: int) -> bool:
+    """Shapes the persistent packed-weight kernel takes (the rest go through ``arcq_linear_forward``)."""
+    return group_size == 64 and out_features % 16 == 0 and (in_features * bits // 8) % 16 == 0
+
+
+def packed_weight_gemm(xhat: torch.Tensor, packed_w, w_center, w_scale, w_code_sum, w_codebook, bias, bits: int,
+                       group_size: int, out_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """fp16 reconstructed activation [M,K] x packed weight -> [M,N].
+
+    Steps 3-5 of the reference's on-the-fly forward (arcq_packed_on_the_fly.py:147-161: Triton weight
+    unpack, bias cast, cuBLAS ``F.linear``) as one kernel; ``xhat`` is the output of
+    ``quantize_activation_dequant(..., out_dtype=torch.float16)``.
+    """
+    lib = _cabi.load()
+    xhat = _dev(xhat, "xhat", torch.float16)
+    packed_w = _dev(packed_w, "packed_w", torch.uint8)
+    f = [_dev(t, n, torch.float32) for t, n in ((w_center, "w_center"), (w_scale, "w_scale"),
+                                                (w_code_sum, "w_code_sum"), (w_codebook, "w_codebook"))]
+    if out_dtype not in (torch.float32, torch.float16):
+        raise RuntimeError("out_dtype must be float32 or float16")
+    M, K = xhat.shape
+    N = packed_w.shape[0]
+    if packed_w.shape[1] != packed_cols(K, bits) or tuple(f[0].shape) != (N, K // group_size):
+        raise RuntimeError(f"packed weight {tuple(packed_w.shape)} / stats {tuple(f[0].shape)} do not match K={K}")
+    b = None
+    if bias is not None and bias.numel() > 0:
+        b = _dev(bias, "bias", torch.float32)
+        if b.numel() != N:
+            raise RuntimeError("bias must have out_features entries")
+    y = torch.empty((M, N), dtype=out_dtype, device=xhat.device)
+    if M == 0:
+        return y
+    rc = lib.arcq_packed_weight_gemm(xhat.data_ptr(), packed_w.data_ptr(), f[0].data_ptr(), f[1].data_ptr(),
+                                     f[2].data_ptr(), f[3].data_ptr(), b.data_ptr() if b is not None else None,
+                                     bits, group_size, M, N, K, y.data_ptr(), _DT[out_dtype], _stream())
+    _check(rc, "arcq_packed_weight_gemm")
     return y
 
 

@@ -259,12 +259,23 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
         if shape[-1] != self.in_features:
             raise ValueError(f"expected last dim {self.in_features}, got {shape[-1]}")
         x2 = x.reshape(-1, self.in_features).to(device=self.packed_weight_codes.device, dtype=torch.float16).contiguous()
-        packed_x, mu, sg, cs = ops.quantize_activation(x2, self.activation_thresholds, self.activation_codebook,
-                                                       self.bits, self.group_size)
-        y = ops.arcq_linear_forward(packed_x, mu, sg, cs, self.packed_weight_codes, self.weight_center,
-                                    self.weight_scale, self.weight_code_sum, self.activation_codebook,
-                                    self.weight_codebook, self.bias_tensor if self.bias_tensor.numel() else None,
-                                    self.bits, self.group_size, self.in_features, self.out_features, torch.float16)
+        bias = self.bias_tensor if self.bias_tensor.numel() else None
+        if ops.packed_weight_gemm_supported(self.in_features, self.out_features, self.bits, self.group_size):
+            # the reference's own data flow: fp16 activation quantised and reconstructed (its step 2),
+            # then weight unpack + contraction + bias (its steps 3-5) in one persistent kernel
+            x_hat = ops.quantize_activation_dequant(x2, self.activation_thresholds, self.activation_codebook,
+                                                    self.bits, self.group_size, torch.float16)
+            y = ops.packed_weight_gemm(x_hat, self.packed_weight_codes, self.weight_center, self.weight_scale,
+                                       self.weight_code_sum, self.weight_codebook, bias, self.bits,
+                                       self.group_size, torch.float16)
+        else:
+            # shapes the persistent kernel does not take (e.g. 3-bit rows of 72 bytes): packed codes both sides
+            packed_x, mu, sg, cs = ops.quantize_activation(x2, self.activation_thresholds, self.activation_codebook,
+                                                           self.bits, self.group_size)
+            y = ops.arcq_linear_forward(packed_x, mu, sg, cs, self.packed_weight_codes, self.weight_center,
+                                        self.weight_scale, self.weight_code_sum, self.activation_codebook,
+                                        self.weight_codebook, bias, self.bits, self.group_size, self.in_features,
+                                        self.out_features, torch.float16)
         return y.reshape(*shape[:-1], self.out_features)
 
     def estimated_persistent_mb(self) -> float:

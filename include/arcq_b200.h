@@ -102,6 +102,24 @@ int arcq_packed_gemm(const uint8_t* packed_x, const float* mu_a, const float* si
                      int64_t M, int64_t N, int64_t K, void* y, int y_dtype, void* stream);
 
 /*
+ * Packed-weight linear on an already reconstructed fp16 activation:
+ *   y[m,n] = bias[n] + sum_k xhat[m,k] * W^[n,k],   W^ rebuilt from packed codes inside the kernel.
+ * This is the data flow of the reference's on-the-fly module: it replaces steps 3-5 of
+ * ARCQPackedLinearOnTheFly.forward, FQ/fair_qat/arcq_packed_on_the_fly.py:147-161 -- the Triton
+ * weight unpack (FQ/fair_qat/arcq_packed_triton.py:77-120), the fp16 bias cast and the cuBLAS
+ * F.linear -- with one persistent kernel (TMA-staged operands, tcgen05 MMA, no fp16 weight in HBM).
+ * xhat is what arcq_act_quant writes to xhat_out with xhat_dtype = ARCQ_DT_F16 (the reference's step 2,
+ * dequant_activation_triton, FQ/fair_qat/arcq_packed_triton.py:181-215).
+ *   xhat fp16 [M,K], 16-byte aligned;  packed_w [N, K*bits/8] with K*bits/8 a multiple of 16;
+ *   N % 16 == 0; group_size must be 64; y [M,N] fp16 or fp32.
+ * Shapes outside these limits return ARCQ_E_UNSUPPORTED (use arcq_packed_gemm).
+ */
+int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const float* mu_w,
+                            const float* sigma_w, const float* codesum_w, const float* w_codebook,
+                            const float* bias, int bits, int group_size, int64_t M, int64_t N, int64_t K,
+                            void* y, int y_dtype, void* stream);
+
+/*
  * Unpack codes to one byte per code.  Replaces unpack_codes_u8_cuda,
  * EXT/arcq_pack_kernel.cu:136-157 (kernel :74-90); the int64 variant
  * unpack_codes_cuda (:113-134) is this plus a widening on the host side.

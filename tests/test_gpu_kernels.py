@@ -81,15 +81,18 @@ def test_act_quant_matches_oracle_all_dtypes(pkg, oracle, cuda_device, bits, dty
 def test_act_quant_ties_go_to_the_lower_code(pkg, cuda_device):
     # a value exactly on a threshold takes the lower code (count of thresholds strictly below)
     cb = np.arange(-8, 8, dtype=np.float32) * 0.25
-    th = (cb[:-1] + cb[1:]) / 2
+    th = ((cb[:-1] + cb[1:]) / 2).astype(np.float32)
     x = np.zeros((1, 64), np.float32)
     x[0, :32], x[0, 32:] = -1.0, 1.0                # mean 0, scale sqrt(1+1e-6) -> t = +-0.9999995
-    th2 = th.copy()
     t_pos = np.float32(1.0) / np.sqrt(np.float32(1.0) + np.float32(1e-6), dtype=np.float32)
-    th2[10] = t_pos                                   # threshold exactly at t
-    p, *_ = pkg.ops.quantize_activation(_t(x, cuda_device), _t(th2, cuda_device), _t(cb, cuda_device), 4, 64)
+    th[11] = t_pos                                    # 0.625 < t_pos < 1.125: still sorted, exactly at t
+    assert np.all(np.diff(th) > 0)
+    p, *_ = pkg.ops.quantize_activation(_t(x, cuda_device), _t(th, cuda_device), _t(cb, cuda_device), 4, 64)
     codes = pkg.ops.unpack_codes_u8(p, 4, 64).cpu().numpy()[0]
-    assert int(codes[63]) == int((th2 < t_pos).sum()) == 10
+    assert int(codes[63]) == int((th < t_pos).sum()) == 11      # not 12: the tie stays below
+    th[11] = np.nextafter(t_pos, np.float32(0))                 # one ulp lower: now strictly below t
+    p, *_ = pkg.ops.quantize_activation(_t(x, cuda_device), _t(th, cuda_device), _t(cb, cuda_device), 4, 64)
+    assert int(pkg.ops.unpack_codes_u8(p, 4, 64).cpu().numpy()[0, 63]) == 12
 
 
 def test_act_quant_full_size_properties(pkg, cuda_device):
@@ -256,3 +259,75 @@ def test_packed_gemm_full_size_properties(pkg, cuda_device):
     _report("packed_gemm_full_size", M=M, K=K, N=N, max_abs_over_rms=err)
     assert err < TOL
     assert pkg.ops.device_status() == 0
+
+
+# ------------------------------------------------------------------ packed-weight GEMM (fp16 activation operand)
+def _pw_case(pkg, oracle, dev, X, W, b, a_th, a_cb, w_th, w_cb, bits, out_dtype):
+    y_ref, it = oracle.fake_quant_linear(X, W, b, a_th, a_cb, w_th, w_cb, 64)
+    xh = pkg.ops.quantize_activation_dequant(_t(X, dev), _t(a_th, dev), _t(a_cb, dev), bits, 64, torch.float16)
+    assert torch.equal(xh.cpu(), torch.from_numpy(oracle.dequant(it["act_codes"], it["act_mu"], it["act_sigma"],
+                                                               a_cb, 64)).half())
+    y = pkg.ops.packed_weight_gemm(xh, _t(oracle.pack(it["w_codes"], bits), dev), _t(it["w_mu"], dev),
+                                   _t(it["w_sigma"], dev), _t(it["w_code_sum"], dev), _t(w_cb, dev),
+                                   None if b is None else _t(b, dev), bits, 64, out_dtype)
+    assert pkg.ops.device_status() == 0, "a bounded wait in the persistent GEMM ran out"
+    rms = float(np.sqrt((y_ref.astype(np.float64) ** 2).mean()))
+    return y, y_ref, rms
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("name", ["c1_w4a4", "c1_w3a3", "edge_k1536_w4a4"])
+def test_packed_weight_gemm_vs_fake_quant_reference(pkg, oracle, golden, cuda_device, name, out_dtype):
+    g = golden(name)
+    y, y_ref, rms = _pw_case(pkg, oracle, cuda_device, g["X"], g["W"], g["b"], g["act_thresholds"], g["act_codebook"],
+                             g["w_thresholds"], g["w_codebook"], g["bits"], out_dtype)
+    yn = y.float().cpu().numpy()
+    err = float(np.abs(yn - y_ref).max() / rms)
+    err_ref = float(np.abs(yn[::16, ::4] - g["y_ref_sub"]).max() / float(g["y_ref_rms"]))
+    _report("packed_weight_gemm", case=name, out=str(out_dtype), max_abs_over_rms=err, vs_reference_fixture=err_ref)
+    assert err < TOL and err_ref < TOL, f"max|dy|/rms = {err:.3e}"
+
+
+@pytest.mark.parametrize("bits", [4, 3, 2])
+@pytest.mark.parametrize("M,K,N", [(1, 64, 16), (5, 128, 32), (129, 128, 48), (197, 192, 576), (300, 384, 1152),
+                                   (1000, 384, 384), (64, 768, 2304), (257, 1536, 384), (700, 3072, 768)])
+def test_packed_weight_gemm_shapes(pkg, oracle, cuda_device, bits, M, K, N):
+    if not pkg.ops.packed_weight_gemm_supported(K, N, bits, 64):
+        pytest.skip("shape is routed to the packed-codes kernel")
+    rng = np.random.default_rng(M * 5 + K + N + bits)
+    X = rng.standard_normal((M, K), dtype=np.float32)
+    X[:, rng.permutation(K)[:2]] *= 20
+    W = (rng.standard_normal((N, K), dtype=np.float32) * 0.02).astype(np.float32)
+    b = (rng.standard_normal(N, dtype=np.float32) * 0.01).astype(np.float32) if (M + N) % 2 else None
+    a_cb, a_th = oracle.calibrate(X, bits)
+    w_cb, w_th = oracle.calibrate(W, bits)
+    y, y_ref, rms = _pw_case(pkg, oracle, cuda_device, X, W, b, a_th, a_cb, w_th, w_cb, bits, torch.float16)
+    err = float(np.abs(y.float().cpu().numpy() - y_ref).max() / rms)
+    _report("packed_weight_gemm_shapes", bits=bits, M=M, K=K, N=N, max_abs_over_rms=err)
+    assert err < TOL, f"max|dy|/rms = {err:.3e}"
+
+
+def test_packed_weight_gemm_full_size_properties(pkg, cuda_device):
+    # DeiT-S at batch 64: fc1 (weights stay resident in shared memory) and fc2 (weights stream)
+    dev = cuda_device
+    gen = torch.Generator().manual_seed(13)
+    cb = torch.linspace(-2.6, 2.6, 16, device=dev)
+    th = (cb[:-1] + cb[1:]) / 2
+    for (M, K, N) in [(64 * 197, 384, 1536), (64 * 197, 1536, 384), (64 * 197, 384, 1152)]:
+        x = torch.randn(M, K, generator=gen).half().to(dev)
+        w = (torch.randn(N, K, generator=gen) * 0.02).to(dev)
+        bias = (torch.randn(N, generator=gen) * 0.01).to(dev)
+        pw, mw, sw, cw = pkg.ops.quantize_activation(w, th, cb, 4, 64)
+        xh = pkg.ops.quantize_activation_dequant(x, th, cb, 4, 64, torch.float16)
+        f = lambda a, b: pkg.ops.packed_weight_gemm(a, pw, mw, sw, cw, cb, b, 4, 64, torch.float32)  # noqa: E731
+        y0, yb = f(xh, None), f(xh, bias)
+        assert torch.allclose(yb - y0, bias.expand_as(y0), atol=1e-5)
+        perm = torch.randperm(M, generator=gen).to(dev)
+        assert torch.equal(f(xh[perm].contiguous(), None), y0[perm])          # rows do not depend on their tile
+        assert torch.equal(f(xh[300:497].contiguous(), None), y0[300:497])    # nor on the batch size
+        wa = pkg.ops.dequant(pw, mw, sw, cw, cb, 4, 64, torch.float32)
+        ref = xh.double() @ wa.double().T
+        err = float((y0.double() - ref).abs().max() / ref.pow(2).mean().sqrt())
+        _report("packed_weight_gemm_full_size", M=M, K=K, N=N, max_abs_over_rms=err)
+        assert err < 5e-3                                                       # only W^ rounding to fp16 differs
+        assert pkg.ops.device_status() == 0

@@ -174,6 +174,11 @@ def test_c_abi_rejects_bad_arguments_before_any_launch(pkg):
     assert lib.arcq_packed_gemm(*args, 4, 64, 1, 12, 64, p, 1, None) == E_SHAPE      # N % 8
     assert lib.arcq_packed_gemm(*args, 4, 64, 1, 16, 96, p, 1, None) == E_SHAPE      # K % 64
     assert lib.arcq_packed_gemm(*args, 4, 64, 1, 16, 64, p, 2, None) == E_ARG        # bf16 out not built
+    a7 = [p] * 7
+    assert lib.arcq_packed_weight_gemm(*a7, 4, 64, 1, 24, 64, p, 1, None) == E_UNSUP      # N % 16
+    assert lib.arcq_packed_weight_gemm(*a7, 3, 64, 1, 64, 192, p, 1, None) == E_UNSUP     # 72-byte packed rows
+    assert lib.arcq_packed_weight_gemm(*a7, 4, 64, 1, 64, 100, p, 1, None) == E_SHAPE
+    assert lib.arcq_packed_weight_gemm(None, *a7[1:], 4, 64, 1, 64, 64, p, 1, None) == E_ARG
     assert lib.arcq_unpack_codes(p, 1, 8, 7, p, None) == E_ARG
     assert lib.arcq_pack_codes(None, 1, 8, 4, p, None) == E_ARG
     assert lib.arcq_dequant(p, p, p, p, p, 4, 64, 1, 100, p, 1, None) == E_SHAPE
