@@ -1,0 +1,319 @@
+// Activation quantizer, second design: one thread per 64-element group, inputs staged through shared
+// memory with 16-byte cp.async (coalesced, double buffered), no warp shuffles and no division.
+//
+// Summation order.  With a whole group in one thread's registers the reference's (torch CPU) order
+//   v[l] = ((x[l]+x[32+l]) + (x[8+l]+x[40+l])) + (x[16+l]+x[48+l])) + (x[24+l]+x[56+l]),  l = 0..7
+//   sum  = ((((((v0+v1)+v2)+v3)+v4)+v5)+v6)+v7
+// is plain local arithmetic.
+//
+// Exact code without dividing.  The code of an element is the number of thresholds th with
+// th < RN(r/s), r = x - mean and s = scale both fp32, RN the IEEE division.  Let h be half the gap
+// from th to the next fp32 number above it, b = th + h the (real) rounding boundary.  Then
+//   RN(r/s) > th  <=>  r/s > b            (r/s == b is impossible: b has 25 significant bits with the
+//                                          last one set, so b*s is never an fp32 number)
+//                 <=>  r > b*s            (s > 0)
+//                 <=>  r > RD(b*s)        (r is fp32; RD = round toward -inf)
+// and RD(b*s) = fma_rd(th, s, h*s) because h is a power of two, so h*s is exact.  Each thread builds
+// its group's 15 limits T_i = fma_rd(th_i, s, h_i*s) once (30 instructions for 64 elements) in a
+// private column of a shared-memory table -- column = thread, so any index is conflict free -- and
+// finds each code by a 4-step binary search of r in that column.  Thresholds too close to zero for
+// h*s to be exact switch the kernel to comparing the IEEE quotient against th itself.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include "ptx.cuh"
+#include "act_quant.cuh"
+
+namespace arcq {
+
+constexpr int kAq2Threads = 128;
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+template <typename XH> __device__ __forceinline__ uint32_t aq2_pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t aq2_pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t aq2_pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t aq2_pack2<float>(float a, float) { return __float_as_uint(a); }
+
+// Sum of 64 registers in the reference's order.
+__device__ __forceinline__ float sum64_ref_order(const float (&x)[64]) {
+  float v[8];
+#pragma unroll
+  for (int l = 0; l < 8; ++l) {
+    const float a0 = __fadd_rn(x[l], x[32 + l]), a1 = __fadd_rn(x[8 + l], x[40 + l]);
+    const float a2 = __fadd_rn(x[16 + l], x[48 + l]), a3 = __fadd_rn(x[24 + l], x[56 + l]);
+    v[l] = __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3);
+  }
+  float s = v[0];
+#pragma unroll
+  for (int l = 1; l < 8; ++l) s = __fadd_rn(s, v[l]);
+  return s;
+}
+
+template <typename T> struct Aq2Row;  // bytes of one staged group row, padded to a conflict-free pitch
+template <> struct Aq2Row<float> { static constexpr int kBytes = 256, kPitch = 272; };
+template <> struct Aq2Row<__half> { static constexpr int kBytes = 128, kPitch = 144; };
+template <> struct Aq2Row<__nv_bfloat16> { static constexpr int kBytes = 128, kPitch = 144; };
+
+template <typename T> __host__ __device__ constexpr size_t aq2_smem_bytes() {
+  return 2 * kAq2Threads * Aq2Row<T>::kPitch + 16 * kAq2Threads * 4 + 3 * 16 * 4 + 16;
+}
+
+// unpack one staged row into 64 floats
+template <typename T> __device__ __forceinline__ void aq2_load_row(const uint8_t* row, float (&x)[64]);
+template <> __device__ __forceinline__ void aq2_load_row<float>(const uint8_t* row, float (&x)[64]) {
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    const uint4 u = *reinterpret_cast<const uint4*>(row + 16 * c);
+    const uint32_t v[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[4 * c + j] = __uint_as_float(v[j]);
+  }
+}
+template <> __device__ __forceinline__ void aq2_load_row<__half>(const uint8_t* row, float (&x)[64]) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint4 u = *reinterpret_cast<const uint4*>(row + 16 * c);
+    const uint32_t v[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v[j]));
+      x[8 * c + 2 * j] = f.x;
+      x[8 * c + 2 * j + 1] = f.y;
+    }
+  }
+}
+template <> __device__ __forceinline__ void aq2_load_row<__nv_bfloat16>(const uint8_t* row, float (&x)[64]) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint4 u = *reinterpret_cast<const uint4*>(row + 16 * c);
+    const uint32_t v[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      x[8 * c + 2 * j] = __uint_as_float(v[j] << 16);
+      x[8 * c + 2 * j + 1] = __uint_as_float(v[j] & 0xFFFF0000u);
+    }
+  }
+}
+
+// XH: type of the optional reconstruction output (same byte size as T is not required).
+template <typename T, int BITS, typename XH, bool WRITE_XHAT>
+__global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* __restrict__ x, long long total_groups,
+                                                                   const float* __restrict__ thresholds,
+                                                                   const float* __restrict__ codebook,
+                                                                   uint8_t* __restrict__ packed,
+                                                                   float* __restrict__ mu_out,
+                                                                   float* __restrict__ sigma_out,
+                                                                   float* __restrict__ codesum_out,
+                                                                   XH* __restrict__ xhat) {
+  constexpr int L = 1 << BITS;
+  constexpr int kPitch = Aq2Row<T>::kPitch, kRowBytes = Aq2Row<T>::kBytes;
+  constexpr int kChunksPerRow = kRowBytes / 16;
+  constexpr int kTableStride = kAq2Threads;  // floats between consecutive table entries of one thread
+  extern __shared__ __align__(16) uint8_t aq2_smem[];
+  uint8_t* const s_stage = aq2_smem;                                                        // 2 x 128 rows
+  float* const s_table = reinterpret_cast<float*>(aq2_smem + 2 * kAq2Threads * kPitch);     // [16][128]
+  float* const s_th = s_table + 16 * kTableStride;                                          // [16]
+  float* const s_h = s_th + 16;                                                             // [16]
+  float* const s_cb = s_h + 16;                                                             // [16]
+  const int tid = threadIdx.x;
+
+  // thresholds, half-gaps to the next float above, codebook; decide whether the division-free test is exact
+  bool exact_r = true;
+  if (tid < 16) {
+    float th = __int_as_float(0x7f800000), h = 0.0f;
+    if (tid < L - 1) {
+      th = thresholds[tid];
+      const int b = __float_as_int(th);
+      const float up = __int_as_float(th > 0.0f ? b + 1 : b - 1);   // next float toward +inf (th != 0)
+      h = __fmul_rn(__fsub_rn(up, th), 0.5f);
+    }
+    s_th[tid] = th;
+    s_h[tid] = h;
+    s_cb[tid] = tid < L ? codebook[tid] : 0.0f;
+  }
+#pragma unroll
+  for (int i = 0; i < L - 1; ++i) exact_r = exact_r && (fabsf(__ldg(thresholds + i)) > 1.0e-15f);
+  __syncthreads();
+
+  const long long tiles = (total_groups + kAq2Threads - 1) / kAq2Threads;
+  float* const my_table = s_table + tid;
+
+  auto issue_tile = [&](long long tile, int buf) {
+    const long long g0 = tile * kAq2Threads;
+    const long long ng = min(static_cast<long long>(kAq2Threads), total_groups - g0);
+    const int nchunks = static_cast<int>(ng) * kChunksPerRow;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(x) + g0 * kRowBytes;
+    const uint32_t dst = smem_u32(s_stage) + buf * kAq2Threads * kPitch;
+#pragma unroll
+    for (int i = 0; i < kChunksPerRow; ++i) {
+      const int q = tid + kAq2Threads * i;
+      if (q < nchunks) cp_async16(dst + (q / kChunksPerRow) * kPitch + (q % kChunksPerRow) * 16, src + q * 16);
+    }
+    cp_async_commit();
+  };
+
+  long long tile = blockIdx.x;
+  int buf = 0;
+  if (tile < tiles) issue_tile(tile, 0);
+  for (; tile < tiles; tile += gridDim.x, buf ^= 1) {
+    const long long next = tile + gridDim.x;
+    if (next < tiles) {
+      issue_tile(next, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    const long long gi = tile * kAq2Threads + tid;
+    const bool valid = gi < total_groups;
+    uint8_t* const row = s_stage + buf * kAq2Threads * kPitch + tid * kPitch;
+    float v[64];
+    if (valid) {
+      aq2_load_row<T>(row, v);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) v[j] = 0.0f;
+    }
+    const float mean = __fdiv_rn(sum64_ref_order(v), 64.0f);
+    float var;
+    {
+      float q[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        v[j] = __fsub_rn(v[j], mean);
+        q[j] = __fmul_rn(v[j], v[j]);
+      }
+      var = __fdiv_rn(sum64_ref_order(q), 64.0f);
+    }
+    const float scale = __fsqrt_rn(__fadd_rn(var, 1.0e-6f));
+
+    // this group's limits in r-space (or the thresholds themselves when dividing)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float t = __int_as_float(0x7f800000);
+      if (i < L - 1) {
+        const float th = s_th[i];
+        t = exact_r ? __fmaf_rd(th, scale, __fmul_rn(s_h[i], scale)) : th;
+      }
+      if (i < L) my_table[i * kTableStride] = t;
+    }
+
+    // Binary search of each residual in this thread's column of the table.  `off` is a byte offset that
+    // accumulates the code (code * kTableStride * 4), so a step is: load, compare, conditional add.
+    uint32_t words[8];
+    const char* const col = reinterpret_cast<const char*>(my_table);
+    constexpr int kStep = kTableStride * 4;
+    auto classify = [&](auto key_of) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t w = 0;
+#pragma unroll
+        for (int j = 7; j >= 0; --j) {
+          const float key = key_of(v[8 * c + j]);
+          int off = 0;
+          if (BITS >= 4) off += (key > *reinterpret_cast<const float*>(col + off + 7 * kStep)) ? 8 * kStep : 0;
+          if (BITS >= 3) off += (key > *reinterpret_cast<const float*>(col + off + 3 * kStep)) ? 4 * kStep : 0;
+          off += (key > *reinterpret_cast<const float*>(col + off + 1 * kStep)) ? 2 * kStep : 0;
+          off += (key > *reinterpret_cast<const float*>(col + off)) ? kStep : 0;
+          // kStep = 512 bytes: code = off >> 9; the codebook entry sits at byte offset code * 4 = off >> 7
+          w = (w << 4) | static_cast<uint32_t>(off >> 9);
+          v[8 * c + j] = *reinterpret_cast<const float*>(reinterpret_cast<const char*>(s_cb) + (off >> 7));
+        }
+        words[c] = w;
+      }
+    };
+    if (exact_r) {
+      classify([](float r) { return r; });
+    } else {
+      classify([scale](float r) { return __fdiv_rn(r, scale); });
+    }
+    const float code_sum = sum64_ref_order(v);
+
+    if (valid) {
+      if (packed != nullptr) {
+        if (BITS == 4) {
+          uint4* o = reinterpret_cast<uint4*>(packed + gi * 32);
+          o[0] = make_uint4(words[0], words[1], words[2], words[3]);
+          o[1] = make_uint4(words[4], words[5], words[6], words[7]);
+        } else if (BITS == 3) {
+          uint32_t s24[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) s24[c] = squeeze_nibbles_3(words[c]);
+          uint32_t* o = reinterpret_cast<uint32_t*>(packed + gi * 24);   // 24 bytes per group: 8-byte aligned
+          uint32_t ow[6];
+#pragma unroll
+          for (int p2 = 0; p2 < 2; ++p2) {                               // 4 chunks (12 bytes) -> 3 words
+            const uint32_t a = s24[4 * p2], b = s24[4 * p2 + 1], c2 = s24[4 * p2 + 2], d = s24[4 * p2 + 3];
+            ow[3 * p2] = a | (b << 24);
+            ow[3 * p2 + 1] = (b >> 8) | (c2 << 16);
+            ow[3 * p2 + 2] = (c2 >> 16) | (d << 8);
+          }
+          uint2* o2 = reinterpret_cast<uint2*>(o);
+          o2[0] = make_uint2(ow[0], ow[1]);
+          o2[1] = make_uint2(ow[2], ow[3]);
+          o2[2] = make_uint2(ow[4], ow[5]);
+        } else {
+          uint32_t ow[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) ow[c] = squeeze_nibbles_2(words[2 * c]) | (squeeze_nibbles_2(words[2 * c + 1]) << 16);
+          *reinterpret_cast<uint4*>(packed + gi * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+      }
+      if (mu_out != nullptr) {
+        mu_out[gi] = mean;
+        sigma_out[gi] = scale;
+        if (codesum_out != nullptr) codesum_out[gi] = code_sum;
+      }
+    }
+
+    if (WRITE_XHAT) {
+      // reconstruction mean + scale*(cb[c] - code_sum/64), rounded step by step like the reference's fp32
+      // tensor ops, written back over this thread's staged row and copied out coalesced by the block
+      static_assert(!WRITE_XHAT || sizeof(XH) <= sizeof(T), "reconstruction must fit the staged row");
+      static_assert(kAq2Threads * 4 == 512, "the code extraction above assumes a 512-byte table step");
+      const float vm = __fdiv_rn(code_sum, 64.0f);
+      constexpr int kOutChunks = 64 * sizeof(XH) / 16;   // 16-byte chunks of one output row
+      constexpr int kPer = 16 / sizeof(XH);               // values per chunk
+#pragma unroll
+      for (int c = 0; c < kOutChunks; ++c) {
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int e = kPer * c + (kPer / 4) * j;
+          const float f0 = __fadd_rn(mean, __fmul_rn(scale, __fsub_rn(v[e], vm)));
+          const float f1 = (kPer == 8) ? __fadd_rn(mean, __fmul_rn(scale, __fsub_rn(v[e + (kPer == 8 ? 1 : 0)], vm))) : 0.0f;
+          o[j] = aq2_pack2<XH>(f0, f1);
+        }
+        *reinterpret_cast<uint4*>(row + 16 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      __syncthreads();
+      const long long g0 = tile * kAq2Threads;
+      const int ng = static_cast<int>(min(static_cast<long long>(kAq2Threads), total_groups - g0));
+      uint8_t* dst = reinterpret_cast<uint8_t*>(xhat) + g0 * (64 * sizeof(XH));
+      const uint8_t* sbuf = s_stage + buf * kAq2Threads * kPitch;
+#pragma unroll
+      for (int i = 0; i < kOutChunks; ++i) {
+        const int q = tid + kAq2Threads * i;
+        if (q < ng * kOutChunks)
+          *reinterpret_cast<uint4*>(dst + q * 16) =
+              *reinterpret_cast<const uint4*>(sbuf + (q / kOutChunks) * kPitch + (q % kOutChunks) * 16);
+      }
+    }
+    __syncthreads();  // everybody is done with this buffer before the tile after next is loaded into it
+  }
+}
+
+}  // namespace arcq

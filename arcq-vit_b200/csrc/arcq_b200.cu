@@ -6,10 +6,12 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <stdlib.h>
 
 #include "../../include/arcq_b200.h"
 #include "ptx.cuh"
 #include "act_quant.cuh"
+#include "act_quant_v2.cuh"
 #include "codes.cuh"
 #include "packed_gemm.cuh"
 #include "gemm_ws.cuh"
@@ -32,6 +34,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 __device__ int g_status_word = 0;
+long long* g_trace_buf = nullptr;   // set by arcq_debug_trace; 64 timestamps per CTA
 
 int* status_ptr() {
   // one address per device; looked up once per device and cached
@@ -58,6 +61,14 @@ int sm_count() {
     cached_dev = dev;
   }
   return sms;
+}
+
+// Tuning overrides for experiments (unset in normal use): ARCQ_WS_BN, ARCQ_WS_SA, ARCQ_WS_WS,
+// ARCQ_WS_STATIONARY, ARCQ_WS_NBB, ARCQ_WS_GRID,
+// ARCQ_WS_TMA_STORE, ARCQ_WS_ROTATE, ARCQ_ACT_QUANT_V1.
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v != nullptr && *v != 0) ? atoi(v) : dflt;
 }
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
@@ -89,10 +100,44 @@ cudaError_t launch_act_quant(const void* x, long long groups, const float* th, c
   return cudaGetLastError();
 }
 
+// Second-design quantizer (one thread per group, staged loads): taken when the buffers are aligned for its
+// 16-byte accesses and the reconstruction, if asked for, has the input's element type.
+template <typename T, int BITS>
+cudaError_t launch_act_quant_v2(const void* x, long long groups, const float* th, const float* cb, uint8_t* packed,
+                                float* mu, float* sg, float* cs, void* xhat, cudaStream_t st) {
+  const size_t smem = arcq::aq2_smem_bytes<T>();
+  const long long tiles = (groups + arcq::kAq2Threads - 1) / arcq::kAq2Threads;
+  const long long cap = static_cast<long long>(sm_count()) * 4;
+  const int grid = static_cast<int>(tiles < cap ? tiles : cap);
+  const T* xt = static_cast<const T*>(x);
+  cudaError_t e;
+  if (xhat == nullptr) {
+    auto k = arcq::act_quant_v2_kernel<T, BITS, T, false>;
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    k<<<grid, arcq::kAq2Threads, smem, st>>>(xt, groups, th, cb, packed, mu, sg, cs, nullptr);
+  } else {
+    auto k = arcq::act_quant_v2_kernel<T, BITS, T, true>;
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    k<<<grid, arcq::kAq2Threads, smem, st>>>(xt, groups, th, cb, packed, mu, sg, cs, static_cast<T*>(xhat));
+  }
+  return cudaGetLastError();
+}
+
 template <typename T>
-cudaError_t dispatch_act_quant_bits(int bits, const void* x, long long groups, const float* th, const float* cb,
-                                    uint8_t* packed, float* mu, float* sg, float* cs, void* xhat, int xhat_dtype,
-                                    cudaStream_t st) {
+cudaError_t dispatch_act_quant_bits(int bits, const void* x, int x_dtype, long long groups, const float* th,
+                                    const float* cb, uint8_t* packed, float* mu, float* sg, float* cs, void* xhat,
+                                    int xhat_dtype, cudaStream_t st) {
+  const bool v2 = env_int("ARCQ_ACT_QUANT_V1", 0) == 0 && aligned(x, 16) && (packed == nullptr || aligned(packed, 16)) &&
+                  (xhat == nullptr || (xhat_dtype == x_dtype && aligned(xhat, 16)));
+  if (v2) {
+    switch (bits) {
+      case 4: return launch_act_quant_v2<T, 4>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
+      case 3: return launch_act_quant_v2<T, 3>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
+      default: return launch_act_quant_v2<T, 2>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
+    }
+  }
   switch (bits) {
     case 4: return launch_act_quant<T, 4>(x, groups, th, cb, packed, mu, sg, cs, xhat, xhat_dtype, st);
     case 3: return launch_act_quant<T, 3>(x, groups, th, cb, packed, mu, sg, cs, xhat, xhat_dtype, st);
@@ -172,20 +217,30 @@ bool choose_ws_config(long long M, long long N, long long K, int bits, WsConfig*
     if (ctas * 4 >= 3LL * sms) { best_bn = bn; best_ctas = ctas; break; }  // first (widest) that fills 3/4 of the SMs
     if (ctas > best_ctas) { best_ctas = ctas; best_bn = bn; }
   }
+  const int force_bn = env_int("ARCQ_WS_BN", 0);
+  if (force_bn > 0 && force_bn % 16 == 0 && force_bn <= 256 && N % force_bn == 0) best_bn = force_bn;
   if (best_bn == 0) return false;
   c->bn = best_bn;
   const long long slabs = N / best_bn;
   const long long per = sms / slabs;
   c->grid = static_cast<int>(slabs * (tiles_m < per ? tiles_m : per));
+  const int force_grid = env_int("ARCQ_WS_GRID", 0);
+  if (force_grid > 0 && force_grid <= sms) c->grid = force_grid;
+  const int force_stat = env_int("ARCQ_WS_STATIONARY", -1), force_sa = env_int("ARCQ_WS_SA", 0);
+  const int force_ws = env_int("ARCQ_WS_WS", 0), force_nbb = env_int("ARCQ_WS_NBB", 0);
   // stationary if all G sub-tiles plus two A stages fit
   for (int stationary = 1; stationary >= 0; --stationary) {
-    const int ws = stationary ? G : (G < 3 ? G : 3);
+    if (force_stat >= 0 && stationary != force_stat) continue;
+    int ws = stationary ? G : (G < 3 ? G : 3);
+    if (!stationary && force_ws > 0 && force_ws <= 16) ws = force_ws;
     if (ws > 16) continue;
-    for (int sa = 6; sa >= 2; --sa) {
+    for (int sa = 8; sa >= 2; --sa) {
+      if (force_sa > 0 && sa != force_sa) continue;
       const size_t need = arcq::ws_smem_layout(best_bn, ws, sa, bits).total;
       if (need <= kSmemBudget) {
         c->ws = ws; c->sa = sa; c->stationary = stationary;
         c->nbb = stationary ? 1 : 2;
+        if (force_nbb == 1 || force_nbb == 2) c->nbb = force_nbb;
         c->smem = need + 1024;
         return true;
       }
@@ -201,6 +256,11 @@ extern "C" {
 int arcq_version(void) { return ARCQ_B200_VERSION; }
 
 const char* arcq_last_error_string(void) { return g_err; }
+
+int arcq_debug_trace(void* device_buffer) {
+  g_trace_buf = static_cast<long long*>(device_buffer);
+  return ARCQ_OK;
+}
 
 int arcq_device_status(void) {
   int v = 0, zero = 0;
@@ -233,13 +293,13 @@ int arcq_act_quant(const void* x, int x_dtype, int64_t M, int64_t K, const float
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (x_dtype == ARCQ_DT_F32)
-    e = dispatch_act_quant_bits<float>(bits, x, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
+    e = dispatch_act_quant_bits<float>(bits, x, x_dtype, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
                                        codesum_out, xhat_out, xhat_dtype, st);
   else if (x_dtype == ARCQ_DT_F16)
-    e = dispatch_act_quant_bits<__half>(bits, x, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
+    e = dispatch_act_quant_bits<__half>(bits, x, x_dtype, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
                                         codesum_out, xhat_out, xhat_dtype, st);
   else
-    e = dispatch_act_quant_bits<__nv_bfloat16>(bits, x, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
+    e = dispatch_act_quant_bits<__nv_bfloat16>(bits, x, x_dtype, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
                                                codesum_out, xhat_out, xhat_dtype, st);
   if (e != cudaSuccess) return cuda_fail(e, "act_quant launch");
   return ARCQ_OK;
@@ -330,12 +390,25 @@ int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const flo
                           CU_TENSOR_MAP_SWIZZLE_NONE))
     return fail(ARCQ_E_CUDA, "cuTensorMapEncodeTiled failed for the packed weight");
 
+  // output tensor map for the TMA-store epilogue: 32-row blocks of 64 bytes (32 fp16 / 16 fp32 columns)
+  const int out_cw = (y_dtype == ARCQ_DT_F32) ? 16 : 32;
+  const bool use_tma_store = (cfg.bn % out_cw == 0) && env_int("ARCQ_WS_TMA_STORE", 1) != 0;
+  CUtensorMap tm_y;
+  if (!make_tensor_map_2d(&tm_y, y, (y_dtype == ARCQ_DT_F32) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                          (y_dtype == ARCQ_DT_F32) ? 4 : 2, static_cast<uint64_t>(M), static_cast<uint64_t>(N),
+                          out_cw, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+    return fail(ARCQ_E_CUDA, "cuTensorMapEncodeTiled failed for the output matrix");
+
   arcq::WsParams p;
+  p.tma_store = use_tma_store ? 1 : 0;
+  p.rotate = env_int("ARCQ_WS_ROTATE", 1);
+  p.debug_skip_mma = env_int("ARCQ_WS_SKIP_MMA", 0);
   p.mu_w = mu_w; p.sg_w = sigma_w; p.cs_w = codesum_w; p.cb_w = w_codebook; p.bias = bias; p.y = y;
   p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K); p.G = static_cast<int>(K / 64);
   p.bn = cfg.bn; p.ws = cfg.ws; p.sa = cfg.sa; p.nbb = cfg.nbb; p.stationary = cfg.stationary;
   p.y_f32 = (y_dtype == ARCQ_DT_F32) ? 1 : 0;
   p.status = status_ptr();
+  p.trace = g_trace_buf;
   if (p.status == nullptr) return fail(ARCQ_E_CUDA, "device status word not reachable");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaSuccess;
@@ -344,7 +417,7 @@ int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const flo
     e = cudaFuncSetAttribute(arcq::packed_weight_gemm_ws_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                              static_cast<int>(cfg.smem));                                                          \
     if (e == cudaSuccess) {                                                                                        \
-      arcq::packed_weight_gemm_ws_kernel<B><<<cfg.grid, arcq::kWsThreads, cfg.smem, st>>>(tm_a, tm_w, p);          \
+      arcq::packed_weight_gemm_ws_kernel<B><<<cfg.grid, arcq::kWsThreads, cfg.smem, st>>>(tm_a, tm_w, tm_y, p);          \
       e = cudaGetLastError();                                                                                      \
     }                                                                                                              \
   } while (0)

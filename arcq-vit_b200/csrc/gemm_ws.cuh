@@ -40,7 +40,11 @@ struct WsParams {
   int nbb;        // tiles per batch (1 or 2)
   int stationary; // 1: ring holds all G sub-tiles, filled once
   int y_f32;
+  int debug_skip_mma;  // experiments only: consume the stages without issuing MMAs
+  int rotate;     // 1: slabs walk their tile list from different starting points
+  int tma_store;  // 1: epilogue stages 32-row x 128-byte blocks in shared memory and stores them with TMA
   int* status;
+  long long* trace;  // debugging: per-CTA timestamps (64 slots each), or null
 };
 
 constexpr int kWsThreads = 14 * 32;
@@ -54,14 +58,16 @@ __host__ __device__ constexpr int raw_row_bytes(int bits) { return 2 * 8 * bits;
 
 struct WsSmem {
   // offsets from the 1024-aligned base
-  uint32_t a, w, raw, misc;
+  uint32_t a, w, stage, raw, misc;
   uint32_t total;
 };
+constexpr uint32_t kEpiStageBytes = 4 * 4096;  // 4 epilogue warps x (32 rows x 128 bytes)
 __host__ __device__ inline WsSmem ws_smem_layout(int bn, int ws, int sa, int bits) {
   WsSmem s;
   s.a = 0;
   s.w = s.a + static_cast<uint32_t>(sa) * kStageA;
-  s.raw = s.w + static_cast<uint32_t>(ws) * bn * 128;
+  s.stage = s.w + static_cast<uint32_t>(ws) * bn * 128;
+  s.raw = s.stage + kEpiStageBytes;
   const uint32_t raw_slot = static_cast<uint32_t>(bn) * raw_row_bytes(bits) + 16;  // +16: 3-bit reads may look 3 bytes ahead
   s.misc = s.raw + kRawSlots * ((raw_slot + 127) & ~127u);
   s.total = s.misc + 16 * 4 /*lut*/ + 256 * 4 /*bias*/ + 64 * 8 /*barriers*/ + 16;
@@ -71,13 +77,15 @@ __host__ __device__ inline WsSmem ws_smem_layout(int bn, int ws, int sa, int bit
 template <int BITS>
 __global__ void __launch_bounds__(kWsThreads, 1)
 packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
-                             const WsParams p) {
+                             const __grid_constant__ CUtensorMap tm_y, const WsParams p) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // round up to 1024 bytes by pointer arithmetic, so the compiler still knows this is shared memory
+  uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const WsSmem L = ws_smem_layout(p.bn, p.ws, p.sa, BITS);
   uint8_t* const sA = smem + L.a;
   uint8_t* const sW = smem + L.w;
   uint8_t* const sRaw = smem + L.raw;
+  uint8_t* const sStage = smem + L.stage;
   const uint32_t raw_slot_bytes = (static_cast<uint32_t>(p.bn) * raw_row_bytes(BITS) + 16 + 127) & ~127u;
   float* const s_lut = reinterpret_cast<float*>(smem + L.misc);
   float* const s_bias = s_lut + 16;
@@ -90,6 +98,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   uint64_t* const raw_empty = bars + 50;     // [2]
   uint64_t* const acc_full = bars + 52;      // [2]
   uint64_t* const acc_empty = bars + 54;     // [2]
+  uint64_t* const stats_full = bars + 56;    // [1]
   uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(bars + 64);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -101,8 +110,15 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   const int tiles_m = (p.M + kTileM - 1) / kTileM;
   const int my_tiles = (rank < tiles_m) ? (tiles_m - rank + ctas_in_slab - 1) / ctas_in_slab : 0;
   const int n0 = slab * bn;
+  // The CTAs of different slabs that share a rank walk the same tiles; each slab starts at a different
+  // point of that list so that they do not all ask L2 for the same lines at the same moment.
+  const int rot = (my_tiles > 0 && p.rotate) ? (slab * my_tiles) / n_slabs : 0;
+  auto tile_of = [&](int t) { int q = t + rot; if (q >= my_tiles) q -= my_tiles; return rank + q * ctas_in_slab; };
   const int nbb = p.nbb;
   const bool stationary = p.stationary != 0;
+  // W-stationary: the slab's three statistics arrays (bn x G floats each, contiguous in global memory)
+  // are bulk-copied once into the epilogue staging area, which is idle until the first tile is done.
+  const bool stats_smem = stationary && static_cast<uint32_t>(bn) * G * 12u <= kEpiStageBytes;
 
   if (tid < 16) s_lut[tid] = (tid < (1 << BITS)) ? p.cb_w[tid] : 0.0f;
   for (int i = tid; i < bn; i += kWsThreads) s_bias[i] = (p.bias != nullptr) ? p.bias[n0 + i] : 0.0f;
@@ -111,9 +127,11 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
     for (int i = 0; i < p.ws; ++i) { mbar_init(&w_full[i], kWsProducerWarps); mbar_init(&w_empty[i], 1); }
     for (int i = 0; i < kRawSlots; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kWsProducerWarps); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    mbar_init(stats_full, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_y);
   }
   if (warp == 0) {
     tmem_alloc(s_tmem, 512);
@@ -124,70 +142,107 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   tc_fence_after_sync();
   const uint32_t tmem_base = *s_tmem;
   bool ok = true;
+  long long* const tr = (p.trace != nullptr) ? p.trace + static_cast<long long>(blockIdx.x) * 128 : nullptr;
+  auto stamp = [&](int slot) {
+    if (tr != nullptr && slot < 128) {
+      long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      tr[slot] = t;
+    }
+  };
+  if (tid == 0) stamp(0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA issuer
     if (lane == 0) {
-      uint32_t seq_a = 0, seq_r = 0;
+      // ring positions are advanced incrementally (no division in the loop): slot index + phase bit
+      uint32_t a_slot = 0, a_ph = 1, r_slot = 0, r_ph = 1;     // "empty" barriers: first pass is free
+      const uint32_t sa = p.sa;
+      const int raw_x_step = raw_row_bytes(BITS);
+      if (stats_smem && my_tiles > 0) {
+        const uint32_t sb = static_cast<uint32_t>(bn) * G * 4u;
+        const size_t off = static_cast<size_t>(n0) * G;
+        mbar_arrive_expect_tx(stats_full, 3 * sb);
+        bulk_load_1d(sStage, p.mu_w + off, sb, stats_full);
+        bulk_load_1d(sStage + sb, p.sg_w + off, sb, stats_full);
+        bulk_load_1d(sStage + 2 * sb, p.cs_w + off, sb, stats_full);
+      }
       for (int b0 = 0; b0 < my_tiles && ok; b0 += nbb) {
         const int nb = min(nbb, my_tiles - b0);
         for (int g = 0; g < G && ok; ++g) {
           if ((!stationary || b0 == 0) && (g & 1) == 0) {
-            const uint32_t slot = seq_r % kRawSlots;
-            ok = mbar_wait(&raw_empty[slot], ((seq_r / kRawSlots) & 1) ^ 1);
+            ok = mbar_wait_relaxed(&raw_empty[r_slot], r_ph);
             if (!ok) break;
-            mbar_arrive_expect_tx(&raw_full[slot], static_cast<uint32_t>(bn) * raw_row_bytes(BITS));
-            tma_load_2d(sRaw + slot * raw_slot_bytes, &tm_w, &raw_full[slot], (g >> 1) * raw_row_bytes(BITS), n0);
-            ++seq_r;
+            mbar_arrive_expect_tx(&raw_full[r_slot], static_cast<uint32_t>(bn) * raw_row_bytes(BITS));
+            tma_load_2d(sRaw + r_slot * raw_slot_bytes, &tm_w, &raw_full[r_slot], (g >> 1) * raw_x_step, n0);
+            if (++r_slot == kRawSlots) { r_slot = 0; r_ph ^= 1; }
           }
           for (int j = 0; j < nb; ++j) {
-            const int tile = rank + (b0 + j) * ctas_in_slab;
-            const uint32_t slot = seq_a % p.sa;
-            ok = mbar_wait(&a_empty[slot], ((seq_a / p.sa) & 1) ^ 1);
+            ok = mbar_wait_relaxed(&a_empty[a_slot], a_ph, 32);
             if (!ok) break;
-            mbar_arrive_expect_tx(&a_full[slot], kStageA);
-            tma_load_2d(sA + slot * kStageA, &tm_a, &a_full[slot], g * 64, tile * kTileM);
-            ++seq_a;
+            mbar_arrive_expect_tx(&a_full[a_slot], kStageA);
+            tma_load_2d(sA + a_slot * kStageA, &tm_a, &a_full[a_slot], g * 64, tile_of(b0 + j) * kTileM);
+            if (++a_slot == sa) { a_slot = 0; a_ph ^= 1; }
           }
         }
       }
+      stamp(1);
       if (!ok) atomicExch(p.status, kStatusWsTimeout);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_f16(kTileM, bn);
-      uint32_t seq_a = 0, seq_w = 0, tile_seq = 0;
+      // ring positions advance incrementally; descriptors are a constant high part plus (address >> 4)
+      const uint64_t desc_hi = umma_desc_sw128(0);
+      const uint32_t sa = p.sa, wsn = p.ws;
+      const uint32_t a_base = smem_u32(sA) >> 4, w_base = smem_u32(sW) >> 4;
+      const uint32_t a_step = kStageA >> 4, w_step = static_cast<uint32_t>(bn) * 128 >> 4;
+      uint32_t a_slot = 0, a_ph = 0, a_addr = a_base;
+      uint32_t w_slot = 0, w_ph = 0, w_addr = w_base;
+      uint32_t acc_ph[2] = {1, 1};      // acc_empty phases: first use of each buffer is free
+      uint32_t buf = 0;                 // accumulator buffer of the next tile
       for (int b0 = 0; b0 < my_tiles && ok; b0 += nbb) {
         const int nb = min(nbb, my_tiles - b0);
+        const uint32_t buf0 = buf;
         for (int j = 0; j < nb && ok; ++j) {
-          const uint32_t ts = tile_seq + j;
-          ok = mbar_wait(&acc_empty[ts & 1], ((ts >> 1) & 1) ^ 1);
+          const uint32_t bj = (buf0 + j) & 1;
+          ok = mbar_wait_relaxed(&acc_empty[bj], acc_ph[bj], 32);
+          acc_ph[bj] ^= 1;
         }
         tc_fence_after_sync();
+        stamp(8 + 2 * (b0 / nbb));
         for (int g = 0; g < G && ok; ++g) {
-          const uint32_t wslot = stationary ? static_cast<uint32_t>(g) : seq_w % p.ws;
-          ok = mbar_wait(&w_full[wslot], stationary ? 0u : ((seq_w / p.ws) & 1));
+          if (stationary) { w_slot = g; w_addr = w_base + g * w_step; }
+          ok = mbar_wait(&w_full[w_slot], stationary ? 0u : w_ph);
           if (!ok) break;
-          const uint64_t db = umma_desc_sw128(smem_u32(sW + wslot * bn * 128));
+          const uint64_t db = desc_hi | w_addr;
           for (int j = 0; j < nb; ++j) {
-            const uint32_t slot = seq_a % p.sa;
-            ok = mbar_wait(&a_full[slot], (seq_a / p.sa) & 1);
+            ok = mbar_wait(&a_full[a_slot], a_ph);
             if (!ok) break;
             tc_fence_after_sync();
-            const uint64_t da = umma_desc_sw128(smem_u32(sA + slot * kStageA));
-            const uint32_t d = tmem_base + ((tile_seq + j) & 1) * 256;
+            const uint64_t da = desc_hi | a_addr;
+            const uint32_t d = tmem_base + ((buf0 + j) & 1) * 256;
+            if (!p.debug_skip_mma) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) umma_f16(d, da + 2 * k, db + 2 * k, idesc, (g > 0 || k > 0) ? 1u : 0u);
-            umma_commit(&a_empty[slot]);
-            ++seq_a;
+              for (int k = 0; k < 4; ++k) umma_f16(d, da + 2 * k, db + 2 * k, idesc, (g > 0 || k > 0) ? 1u : 0u);
+              umma_commit(&a_empty[a_slot]);
+            } else {
+              mbar_arrive(&a_empty[a_slot]);
+            }
+            a_addr += a_step;
+            if (++a_slot == sa) { a_slot = 0; a_addr = a_base; a_ph ^= 1; }
           }
-          if (!stationary) umma_commit(&w_empty[wslot]);
-          ++seq_w;
+          if (!stationary) {
+            umma_commit(&w_empty[w_slot]);
+            w_addr += w_step;
+            if (++w_slot == wsn) { w_slot = 0; w_addr = w_base; w_ph ^= 1; }
+          }
         }
         if (ok)
-          for (int j = 0; j < nb; ++j) umma_commit(&acc_full[(tile_seq + j) & 1]);
-        tile_seq += nb;
+          for (int j = 0; j < nb; ++j) umma_commit(&acc_full[(buf0 + j) & 1]);
+        stamp(9 + 2 * (b0 / nbb));
+        buf = (buf0 + nb) & 1;
       }
       if (!ok) atomicExch(p.status, kStatusWsTimeout);
     }
@@ -196,14 +251,65 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
     const int lq = warp & 3;  // tensor-memory lane quarter this warp may read
     uint32_t tile_seq = 0;
     for (int t = 0; t < my_tiles && ok; ++t, ++tile_seq) {
-      const int tile = rank + t * ctas_in_slab;
+      const int tile = tile_of(t);
       const uint32_t buf = tile_seq & 1;
-      ok = mbar_wait(&acc_full[buf], (tile_seq >> 1) & 1);
+      ok = mbar_wait_relaxed(&acc_full[buf], (tile_seq >> 1) & 1, 128);
       if (!ok) break;
       tc_fence_after_sync();
+      if (warp == 2 && lane == 0) stamp(32 + 2 * t);
       const long long m = static_cast<long long>(tile) * kTileM + lq * 32 + lane;
       const bool row_ok = m < p.M;
       const uint32_t t_row = tmem_base + buf * 256 + (static_cast<uint32_t>(lq * 32) << 16);
+      if (p.tma_store) {
+        // 32 rows x 64 bytes per step (32 fp16 or 16 fp32 columns): registers -> staging block with the
+        // 64-byte swizzle (conflict-free 16-byte stores) -> one TMA store.  Two blocks per warp alternate,
+        // so a step only waits for the store issued two steps earlier to have read its block.
+        uint8_t* const stg = sStage + lq * 4096;
+        const int cw = p.y_f32 ? 16 : 32;
+        uint32_t half = 0;
+        for (int c0 = 0; c0 < bn; c0 += cw, half ^= 1) {
+          uint32_t acc[32];
+          if (p.y_f32) {
+            tmem_ld_32x16(t_row + c0, *reinterpret_cast<uint32_t(*)[16]>(&acc[0]));
+          } else {
+            tmem_ld_32x32(t_row + c0, acc);
+          }
+          tmem_ld_wait();
+          if (lane == 0) tma_store_wait_read_1();
+          __syncwarp();
+          uint8_t* const rowp = stg + half * 2048 + lane * 64;
+          const int sw = (lane >> 1) & 3;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 v;
+            if (p.y_f32) {
+              const float4 b4 = *reinterpret_cast<const float4*>(s_bias + c0 + 4 * ch);
+              v.x = __float_as_uint(__uint_as_float(acc[4 * ch]) + b4.x);
+              v.y = __float_as_uint(__uint_as_float(acc[4 * ch + 1]) + b4.y);
+              v.z = __float_as_uint(__uint_as_float(acc[4 * ch + 2]) + b4.z);
+              v.w = __float_as_uint(__uint_as_float(acc[4 * ch + 3]) + b4.w);
+            } else {
+              const float4 b0 = *reinterpret_cast<const float4*>(s_bias + c0 + 8 * ch);
+              const float4 b1 = *reinterpret_cast<const float4*>(s_bias + c0 + 8 * ch + 4);
+              __half2 h0 = __floats2half2_rn(__uint_as_float(acc[8 * ch]) + b0.x, __uint_as_float(acc[8 * ch + 1]) + b0.y);
+              __half2 h1 = __floats2half2_rn(__uint_as_float(acc[8 * ch + 2]) + b0.z, __uint_as_float(acc[8 * ch + 3]) + b0.w);
+              __half2 h2 = __floats2half2_rn(__uint_as_float(acc[8 * ch + 4]) + b1.x, __uint_as_float(acc[8 * ch + 5]) + b1.y);
+              __half2 h3 = __floats2half2_rn(__uint_as_float(acc[8 * ch + 6]) + b1.z, __uint_as_float(acc[8 * ch + 7]) + b1.w);
+              v.x = *reinterpret_cast<uint32_t*>(&h0);
+              v.y = *reinterpret_cast<uint32_t*>(&h1);
+              v.z = *reinterpret_cast<uint32_t*>(&h2);
+              v.w = *reinterpret_cast<uint32_t*>(&h3);
+            }
+            *reinterpret_cast<uint4*>(rowp + ((ch ^ sw) << 4)) = v;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tm_y, stg + half * 2048, n0 + c0, tile * kTileM + lq * 32);
+            tma_store_commit();
+          }
+        }
+      } else
       for (int c0 = 0; c0 < bn; c0 += 32) {
         uint32_t acc[32];
         if (c0 + 32 <= bn) {
@@ -249,41 +355,56 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (warp == 2 && lane == 0) stamp(33 + 2 * t);
     }
+    if (lane == 0) tma_store_wait_all();
     if (!ok && lane == 0) atomicExch(p.status, kStatusWsTimeout);
   } else {
     // ------------------------------------------------------------------ W producers
     const int ptid = tid - 6 * 32;
-    uint32_t seq_r = 0, seq_w = 0;
+    uint32_t r_slot = 0, r_ph = 0, w_slot = 0, w_ph = 1;
     const int fills = stationary ? 1 : (my_tiles + nbb - 1) / nbb;  // how many times the slab is walked
+    // Each thread owns the (row, 16-byte chunk) units u = ptid + 256*i of a sub-tile: row (ptid>>3) + 32*i,
+    // chunk ptid&7.  Statistics come from shared memory when the slab's arrays were staged there
+    // (W-stationary), else from global memory (L2 after the first walk of the slab).
+    const int chunk = ptid & 7;
+    const int units = (bn * 8 + kWsProducerThreads - 1 - ptid) / kWsProducerThreads;
+    const float* const st_mu = reinterpret_cast<const float*>(sStage);
+    const float* const st_sg = st_mu + bn * G;
+    const float* const st_cs = st_sg + bn * G;
+    if (stats_smem && my_tiles > 0) ok = mbar_wait_relaxed(stats_full, 0);
     for (int f = 0; f < fills && ok; ++f) {
       if (my_tiles == 0) break;
       for (int g = 0; g < G && ok; ++g) {
-        const uint32_t rslot = seq_r % kRawSlots;
-        if ((g & 1) == 0) ok = mbar_wait(&raw_full[rslot], (seq_r / kRawSlots) & 1);
-        const uint32_t wslot = stationary ? static_cast<uint32_t>(g) : seq_w % p.ws;
-        if (ok && !stationary) ok = mbar_wait(&w_empty[wslot], ((seq_w / p.ws) & 1) ^ 1);
+        const uint32_t rslot = r_slot;
+        if ((g & 1) == 0) ok = mbar_wait_relaxed(&raw_full[rslot], r_ph);
+        const uint32_t wslot = stationary ? static_cast<uint32_t>(g) : w_slot;
+        if (ok && !stationary) ok = mbar_wait_relaxed(&w_empty[wslot], w_ph);
         if (!ok) break;
-        const uint8_t* raw = sRaw + rslot * raw_slot_bytes + (g & 1) * (8 * BITS);
-        uint8_t* dstw = sW + wslot * bn * 128;
-        for (int u = ptid; u < bn * 8; u += kWsProducerThreads) {
-          const int r = u >> 3, chunk = u & 7;
+        const uint8_t* const raw = sRaw + rslot * raw_slot_bytes + (g & 1) * (8 * BITS);
+        uint8_t* const dstw = sW + wslot * bn * 128;
+#pragma unroll 2
+        for (int i = 0; i < units; ++i) {
+          const int r = (ptid >> 3) + 32 * i;
           const uint8_t* rp = raw + r * raw_row_bytes(BITS);
           uint32_t w;
           if (BITS == 4) {
             w = *reinterpret_cast<const uint32_t*>(rp + 4 * chunk);
           } else if (BITS == 3) {
             const int off = 3 * chunk, al = off & ~3, sh = (off & 3) * 8;  // rp is 8-byte aligned
-            const uint32_t lo = *reinterpret_cast<const uint32_t*>(rp + al);
-            const uint32_t hi = *reinterpret_cast<const uint32_t*>(rp + al + 4);
-            w = spread_3_to_nibbles(__funnelshift_r(lo, hi, sh) & 0xFFFFFFu);
+            w = spread_3_to_nibbles(__funnelshift_r(*reinterpret_cast<const uint32_t*>(rp + al),
+                                                    *reinterpret_cast<const uint32_t*>(rp + al + 4), sh) & 0xFFFFFFu);
           } else {
             w = spread_2_to_nibbles(*reinterpret_cast<const uint16_t*>(rp + 2 * chunk));
           }
-          const long long si = static_cast<long long>(n0 + r) * G + g;
-          const float sigma = __ldg(p.sg_w + si);
-          const float mu_f = fmaf(-sigma, __ldg(p.cs_w + si) * (1.0f / 64.0f), __ldg(p.mu_w + si));
-          rebuild_store8(w, sigma, mu_f, s_lut, dstw + sw128_offset(r, chunk));
+          float sigma, mu, cs;
+          if (stats_smem) {
+            sigma = st_sg[r * G + g]; mu = st_mu[r * G + g]; cs = st_cs[r * G + g];
+          } else {
+            const long long si = static_cast<long long>(n0 + r) * G + g;
+            sigma = __ldg(p.sg_w + si); mu = __ldg(p.mu_w + si); cs = __ldg(p.cs_w + si);
+          }
+          rebuild_store8(w, sigma, fmaf(-sigma, cs * (1.0f / 64.0f), mu), s_lut, dstw + sw128_offset(r, chunk));
         }
         fence_proxy_async_smem();
         __syncwarp();
@@ -291,8 +412,11 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
           mbar_arrive(&w_full[wslot]);
           if ((g & 1) == 1 || g == G - 1) mbar_arrive(&raw_empty[rslot]);
         }
-        if ((g & 1) == 1 || g == G - 1) ++seq_r;
-        ++seq_w;
+        if ((g & 1) == 1 || g == G - 1) {
+          if (++r_slot == kRawSlots) { r_slot = 0; r_ph ^= 1; }
+        }
+        if (!stationary && ++w_slot == static_cast<uint32_t>(p.ws)) { w_slot = 0; w_ph ^= 1; }
+        if (f == 0 && ptid == 0) stamp(2 + (g < 5 ? g : 5));
       }
     }
     if (!ok && lane == 0) atomicExch(p.status, kStatusWsTimeout);

@@ -92,7 +92,7 @@ template <int BITS>
 __global__ void __launch_bounds__(kGemmThreads, 1) packed_gemm_kernel(const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is what the 128-byte swizzle pattern is anchored to
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int bn = p.bn;
   const int stage_b = bn * 128;
   uint8_t* const sA0 = smem;                 // two A stages, then two B stages

@@ -59,6 +59,15 @@ const char* arcq_last_error_string(void);
 int arcq_device_status(void);
 
 /*
+ * Debugging aid: when given a device buffer of 128 int64 per CTA (148 x 128 is enough), the persistent
+ * GEMM kernels launched afterwards write nanosecond timestamps of their pipeline milestones into it
+ * (slot 0 kernel start, 1 loads issued, 2-7 weight sub-tiles rebuilt, 8+2b / 9+2b first MMA / commit of
+ * tile batch b, 32+2t / 33+2t epilogue start / end of tile t).  NULL switches it off (the default).
+ * No reference counterpart.
+ */
+int arcq_debug_trace(void* device_buffer);
+
+/*
  * Activation quantizer: per row and per group of `group_size` consecutive
  * elements computes mean, scale = sqrt(mean(r^2)+1e-6), the code of every
  * element (number of thresholds below (x-mean)/scale) and the sum of code
