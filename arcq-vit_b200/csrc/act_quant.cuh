@@ -32,6 +32,20 @@ template <> __device__ __forceinline__ void store_from_f32<__nv_bfloat16>(__nv_b
   *p = __float2bfloat16_rn(v);
 }
 
+// Optional element-wise op applied to the input before it is quantised (fused from the preceding layer).
+// PRE = 1: exact GELU, 0.5*x*(1+erf(x/sqrt 2)) in fp32, then rounded to the input's element type -- the
+// value a separate GELU kernel would have stored -- so the quantizer sees the same numbers as unfused.
+template <typename T> __device__ __forceinline__ float round_to(float v);
+template <> __device__ __forceinline__ float round_to<float>(float v) { return v; }
+template <> __device__ __forceinline__ float round_to<__half>(float v) { return __half2float(__float2half_rn(v)); }
+template <> __device__ __forceinline__ float round_to<__nv_bfloat16>(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+template <typename T, int PRE> __device__ __forceinline__ float pre_op(float x) {
+  if (PRE == 1) return round_to<T>(x * 0.5f * (1.0f + erff(x * 0.70710678118654752440f)));
+  return x;
+}
+
 // Sum of the value held by the 8 lanes of an octet, lane 0 first, as a chain of fp32 additions.
 __device__ __forceinline__ float octet_chain_sum(float p, int octet_base) {
   float s = __shfl_sync(0xffffffffu, p, octet_base);
@@ -67,7 +81,7 @@ __device__ __forceinline__ uint32_t squeeze_nibbles_2(uint32_t w) {
 // One warp handles 4 consecutive groups per step (8 lanes per group).  Groups are numbered
 // row-major over [M, K/64]; with K a multiple of 64 the input, the packed output and the statistics
 // are all contiguous in that numbering.
-template <typename T, int BITS, typename XH, bool WRITE_XHAT>
+template <typename T, int BITS, typename XH, bool WRITE_XHAT, int PRE = 0>
 __global__ void __launch_bounds__(256) act_quant_kernel(const T* __restrict__ x, long long total_groups,
                                                         const float* __restrict__ thresholds,
                                                         const float* __restrict__ codebook,
@@ -99,7 +113,7 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const T* __restrict__ x,
 
     float v[8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) v[c] = load_f32<T>(xg + 8 * c);
+    for (int c = 0; c < 8; ++c) v[c] = pre_op<T, PRE>(load_f32<T>(xg + 8 * c));
 
     // mean
     float a0 = __fadd_rn(v[0], v[4]), a1 = __fadd_rn(v[1], v[5]);

@@ -108,7 +108,7 @@ template <> __device__ __forceinline__ void aq2_load_row<__nv_bfloat16>(const ui
 }
 
 // XH: type of the optional reconstruction output (same byte size as T is not required).
-template <typename T, int BITS, typename XH, bool WRITE_XHAT>
+template <typename T, int BITS, typename XH, bool WRITE_XHAT, int PRE = 0>
 __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* __restrict__ x, long long total_groups,
                                                                    const float* __restrict__ thresholds,
                                                                    const float* __restrict__ codebook,
@@ -183,6 +183,10 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
     float v[64];
     if (valid) {
       aq2_load_row<T>(row, v);
+      if (PRE != 0) {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) v[j] = pre_op<T, PRE>(v[j]);
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < 64; ++j) v[j] = 0.0f;

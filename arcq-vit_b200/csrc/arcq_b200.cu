@@ -80,21 +80,21 @@ int grid_for(long long work_items, int per_block, int blocks_per_sm) {
   return static_cast<int>(need < cap ? need : cap);
 }
 
-template <typename T, int BITS>
+template <typename T, int BITS, int PRE = 0>
 cudaError_t launch_act_quant(const void* x, long long groups, const float* th, const float* cb, uint8_t* packed,
                              float* mu, float* sg, float* cs, void* xhat, int xhat_dtype, cudaStream_t st) {
   const int grid = grid_for((groups + 3) / 4, 8, 8);
   const T* xt = static_cast<const T*>(x);
   if (xhat == nullptr) {
-    arcq::act_quant_kernel<T, BITS, float, false><<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, nullptr);
+    arcq::act_quant_kernel<T, BITS, float, false, PRE><<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, nullptr);
   } else if (xhat_dtype == ARCQ_DT_F32) {
-    arcq::act_quant_kernel<T, BITS, float, true>
+    arcq::act_quant_kernel<T, BITS, float, true, PRE>
         <<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, static_cast<float*>(xhat));
   } else if (xhat_dtype == ARCQ_DT_F16) {
-    arcq::act_quant_kernel<T, BITS, __half, true>
+    arcq::act_quant_kernel<T, BITS, __half, true, PRE>
         <<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, static_cast<__half*>(xhat));
   } else {
-    arcq::act_quant_kernel<T, BITS, __nv_bfloat16, true>
+    arcq::act_quant_kernel<T, BITS, __nv_bfloat16, true, PRE>
         <<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, static_cast<__nv_bfloat16*>(xhat));
   }
   return cudaGetLastError();
@@ -102,7 +102,7 @@ cudaError_t launch_act_quant(const void* x, long long groups, const float* th, c
 
 // Second-design quantizer (one thread per group, staged loads): taken when the buffers are aligned for its
 // 16-byte accesses and the reconstruction, if asked for, has the input's element type.
-template <typename T, int BITS>
+template <typename T, int BITS, int PRE = 0>
 cudaError_t launch_act_quant_v2(const void* x, long long groups, const float* th, const float* cb, uint8_t* packed,
                                 float* mu, float* sg, float* cs, void* xhat, cudaStream_t st) {
   const size_t smem = arcq::aq2_smem_bytes<T>();
@@ -112,12 +112,12 @@ cudaError_t launch_act_quant_v2(const void* x, long long groups, const float* th
   const T* xt = static_cast<const T*>(x);
   cudaError_t e;
   if (xhat == nullptr) {
-    auto k = arcq::act_quant_v2_kernel<T, BITS, T, false>;
+    auto k = arcq::act_quant_v2_kernel<T, BITS, T, false, PRE>;
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     k<<<grid, arcq::kAq2Threads, smem, st>>>(xt, groups, th, cb, packed, mu, sg, cs, nullptr);
   } else {
-    auto k = arcq::act_quant_v2_kernel<T, BITS, T, true>;
+    auto k = arcq::act_quant_v2_kernel<T, BITS, T, true, PRE>;
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     k<<<grid, arcq::kAq2Threads, smem, st>>>(xt, groups, th, cb, packed, mu, sg, cs, static_cast<T*>(xhat));
@@ -125,23 +125,27 @@ cudaError_t launch_act_quant_v2(const void* x, long long groups, const float* th
   return cudaGetLastError();
 }
 
-template <typename T>
+template <typename T, int PRE>
 cudaError_t dispatch_act_quant_bits(int bits, const void* x, int x_dtype, long long groups, const float* th,
                                     const float* cb, uint8_t* packed, float* mu, float* sg, float* cs, void* xhat,
                                     int xhat_dtype, cudaStream_t st) {
-  const bool v2 = env_int("ARCQ_ACT_QUANT_V1", 0) == 0 && aligned(x, 16) && (packed == nullptr || aligned(packed, 16)) &&
+  // The one-thread-per-group kernel needs enough groups to fill the machine (148 SMs x 4 blocks x 128
+  // threads); below that the 8-lanes-per-group kernel has 8 times the parallelism and lower latency.
+  const bool enough = groups >= static_cast<long long>(sm_count()) * 4 * arcq::kAq2Threads / 2;
+  const bool v2 = enough && env_int("ARCQ_ACT_QUANT_V1", 0) == 0 && aligned(x, 16) &&
+                  (packed == nullptr || aligned(packed, 16)) &&
                   (xhat == nullptr || (xhat_dtype == x_dtype && aligned(xhat, 16)));
   if (v2) {
     switch (bits) {
-      case 4: return launch_act_quant_v2<T, 4>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
-      case 3: return launch_act_quant_v2<T, 3>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
-      default: return launch_act_quant_v2<T, 2>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
+      case 4: return launch_act_quant_v2<T, 4, PRE>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
+      case 3: return launch_act_quant_v2<T, 3, PRE>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
+      default: return launch_act_quant_v2<T, 2, PRE>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
     }
   }
   switch (bits) {
-    case 4: return launch_act_quant<T, 4>(x, groups, th, cb, packed, mu, sg, cs, xhat, xhat_dtype, st);
-    case 3: return launch_act_quant<T, 3>(x, groups, th, cb, packed, mu, sg, cs, xhat, xhat_dtype, st);
-    default: return launch_act_quant<T, 2>(x, groups, th, cb, packed, mu, sg, cs, xhat, xhat_dtype, st);
+    case 4: return launch_act_quant<T, 4, PRE>(x, groups, th, cb, packed, mu, sg, cs, xhat, xhat_dtype, st);
+    case 3: return launch_act_quant<T, 3, PRE>(x, groups, th, cb, packed, mu, sg, cs, xhat, xhat_dtype, st);
+    default: return launch_act_quant<T, 2, PRE>(x, groups, th, cb, packed, mu, sg, cs, xhat, xhat_dtype, st);
   }
 }
 
@@ -271,9 +275,9 @@ int arcq_device_status(void) {
   return v;
 }
 
-int arcq_act_quant(const void* x, int x_dtype, int64_t M, int64_t K, const float* thresholds, const float* codebook,
-                   int bits, int group_size, uint8_t* packed_out, float* mu_out, float* sigma_out, float* codesum_out,
-                   void* xhat_out, int xhat_dtype, void* stream) {
+static int act_quant_impl(int pre, const void* x, int x_dtype, int64_t M, int64_t K, const float* thresholds,
+                          const float* codebook, int bits, int group_size, uint8_t* packed_out, float* mu_out,
+                          float* sigma_out, float* codesum_out, void* xhat_out, int xhat_dtype, void* stream) {
   if (x == nullptr || thresholds == nullptr || codebook == nullptr) return fail(ARCQ_E_BAD_ARG, "null input pointer");
   if (packed_out == nullptr && xhat_out == nullptr) return fail(ARCQ_E_BAD_ARG, "no output requested");
   if ((packed_out != nullptr) != (mu_out != nullptr) || (mu_out != nullptr) != (sigma_out != nullptr))
@@ -292,17 +296,35 @@ int arcq_act_quant(const void* x, int x_dtype, int64_t M, int64_t K, const float
   const long long groups = static_cast<long long>(M) * (K / 64);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
-  if (x_dtype == ARCQ_DT_F32)
-    e = dispatch_act_quant_bits<float>(bits, x, x_dtype, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
-                                       codesum_out, xhat_out, xhat_dtype, st);
+  if (pre == 1) {
+    if (x_dtype != ARCQ_DT_F16) return fail(ARCQ_E_UNSUPPORTED, "the fused GELU is built for fp16 input only");
+    e = dispatch_act_quant_bits<__half, 1>(bits, x, x_dtype, groups, thresholds, codebook, packed_out, mu_out,
+                                           sigma_out, codesum_out, xhat_out, xhat_dtype, st);
+  } else if (x_dtype == ARCQ_DT_F32)
+    e = dispatch_act_quant_bits<float, 0>(bits, x, x_dtype, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
+                                          codesum_out, xhat_out, xhat_dtype, st);
   else if (x_dtype == ARCQ_DT_F16)
-    e = dispatch_act_quant_bits<__half>(bits, x, x_dtype, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
-                                        codesum_out, xhat_out, xhat_dtype, st);
+    e = dispatch_act_quant_bits<__half, 0>(bits, x, x_dtype, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
+                                           codesum_out, xhat_out, xhat_dtype, st);
   else
-    e = dispatch_act_quant_bits<__nv_bfloat16>(bits, x, x_dtype, groups, thresholds, codebook, packed_out, mu_out, sigma_out,
-                                               codesum_out, xhat_out, xhat_dtype, st);
+    e = dispatch_act_quant_bits<__nv_bfloat16, 0>(bits, x, x_dtype, groups, thresholds, codebook, packed_out, mu_out,
+                                                  sigma_out, codesum_out, xhat_out, xhat_dtype, st);
   if (e != cudaSuccess) return cuda_fail(e, "act_quant launch");
   return ARCQ_OK;
+}
+
+int arcq_act_quant(const void* x, int x_dtype, int64_t M, int64_t K, const float* thresholds, const float* codebook,
+                   int bits, int group_size, uint8_t* packed_out, float* mu_out, float* sigma_out, float* codesum_out,
+                   void* xhat_out, int xhat_dtype, void* stream) {
+  return act_quant_impl(0, x, x_dtype, M, K, thresholds, codebook, bits, group_size, packed_out, mu_out, sigma_out,
+                        codesum_out, xhat_out, xhat_dtype, stream);
+}
+
+int arcq_gelu_act_quant(const void* x, int x_dtype, int64_t M, int64_t K, const float* thresholds,
+                        const float* codebook, int bits, int group_size, uint8_t* packed_out, float* mu_out,
+                        float* sigma_out, float* codesum_out, void* xhat_out, int xhat_dtype, void* stream) {
+  return act_quant_impl(1, x, x_dtype, M, K, thresholds, codebook, bits, group_size, packed_out, mu_out, sigma_out,
+                        codesum_out, xhat_out, xhat_dtype, stream);
 }
 
 int arcq_packed_gemm(const uint8_t* packed_x, const float* mu_a, const float* sigma_a, const float* codesum_a,

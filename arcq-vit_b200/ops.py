@@ -43,7 +43,7 @@ def device_status() -> int:
 
 
 def quantize_activation(x: torch.Tensor, thresholds: torch.Tensor, codebook: torch.Tensor, bits: int,
-                        group_size: int, want_code_sum: bool = True):
+                        group_size: int, want_code_sum: bool = True, pre_gelu: bool = False):
     """[M,K] float -> (packed uint8 [M, K*bits/8], center, scale, code_sum fp32 [M, K/group_size]).
 
     Same contract as the reference's ``quantize_activation`` (arcq_activation_kernel.cu:188-237),
@@ -69,16 +69,19 @@ def quantize_activation(x: torch.Tensor, thresholds: torch.Tensor, codebook: tor
     cs = torch.empty_like(mu) if want_code_sum else None
     if M == 0:
         return packed, mu, sg, cs
-    rc = lib.arcq_act_quant(x.data_ptr(), _DT[x.dtype], M, K, th.data_ptr(), cb.data_ptr(), bits, group_size,
-                            packed.data_ptr(), mu.data_ptr(), sg.data_ptr(), cs.data_ptr() if cs is not None else None,
-                            None, 0, _stream())
+    fn = lib.arcq_gelu_act_quant if pre_gelu else lib.arcq_act_quant
+    rc = fn(x.data_ptr(), _DT[x.dtype], M, K, th.data_ptr(), cb.data_ptr(), bits, group_size,
+            packed.data_ptr(), mu.data_ptr(), sg.data_ptr(), cs.data_ptr() if cs is not None else None,
+            None, 0, _stream())
     _check(rc, "arcq_act_quant")
     return packed, mu, sg, cs
 
 
 def quantize_activation_dequant(x: torch.Tensor, thresholds: torch.Tensor, codebook: torch.Tensor, bits: int,
-                                group_size: int, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
-    """[M,K] float -> reconstruction [M,K] (reference: arcq_activation_kernel.cu:286-326)."""
+                                group_size: int, out_dtype: torch.dtype = torch.float32,
+                                pre_gelu: bool = False) -> torch.Tensor:
+    """[M,K] float -> reconstruction [M,K] (reference: arcq_activation_kernel.cu:286-326).
+    ``pre_gelu``: the input is a pre-activation; GELU is applied (and rounded to fp16) on the fly."""
     lib = _cabi.load()
     if x.dim() != 2 or x.dtype not in _DT or out_dtype not in _DT:
         raise RuntimeError("x must be a 2-D float tensor and out_dtype a float dtype")
@@ -89,8 +92,9 @@ def quantize_activation_dequant(x: torch.Tensor, thresholds: torch.Tensor, codeb
     out = torch.empty((M, K), dtype=out_dtype, device=x.device)
     if M == 0:
         return out
-    rc = lib.arcq_act_quant(x.data_ptr(), _DT[x.dtype], M, K, th.data_ptr(), cb.data_ptr(), bits, group_size,
-                            None, None, None, None, out.data_ptr(), _DT[out_dtype], _stream())
+    fn = lib.arcq_gelu_act_quant if pre_gelu else lib.arcq_act_quant
+    rc = fn(x.data_ptr(), _DT[x.dtype], M, K, th.data_ptr(), cb.data_ptr(), bits, group_size,
+            None, None, None, None, out.data_ptr(), _DT[out_dtype], _stream())
     _check(rc, "arcq_act_quant")
     return out
 

@@ -254,7 +254,12 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
                    m.weight_center, m.weight_scale, m.weight_code_sum, m.activation_codebook,
                    m.activation_thresholds, m.bits, m.group_size, m.bias if m.bias.numel() > 0 else None)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    # the module can apply the GELU that precedes it in an MLP block while it quantises its input
+    supports_pre_gelu = True
+
+    def forward(self, x: torch.Tensor, pre_gelu: bool = False) -> torch.Tensor:
+        """``pre_gelu=True``: x is the pre-activation of the GELU in front of this layer; the result
+        equals ``forward(F.gelu(x))`` with the GELU fused into the activation quantizer."""
         shape = x.shape
         if shape[-1] != self.in_features:
             raise ValueError(f"expected last dim {self.in_features}, got {shape[-1]}")
@@ -264,14 +269,14 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
             # the reference's own data flow: fp16 activation quantised and reconstructed (its step 2),
             # then weight unpack + contraction + bias (its steps 3-5) in one persistent kernel
             x_hat = ops.quantize_activation_dequant(x2, self.activation_thresholds, self.activation_codebook,
-                                                    self.bits, self.group_size, torch.float16)
+                                                    self.bits, self.group_size, torch.float16, pre_gelu)
             y = ops.packed_weight_gemm(x_hat, self.packed_weight_codes, self.weight_center, self.weight_scale,
                                        self.weight_code_sum, self.weight_codebook, bias, self.bits,
                                        self.group_size, torch.float16)
         else:
             # shapes the persistent kernel does not take (e.g. 3-bit rows of 72 bytes): packed codes both sides
             packed_x, mu, sg, cs = ops.quantize_activation(x2, self.activation_thresholds, self.activation_codebook,
-                                                           self.bits, self.group_size)
+                                                           self.bits, self.group_size, True, pre_gelu)
             y = ops.arcq_linear_forward(packed_x, mu, sg, cs, self.packed_weight_codes, self.weight_center,
                                         self.weight_scale, self.weight_code_sum, self.activation_codebook,
                                         self.weight_codebook, bias, self.bits, self.group_size, self.in_features,

@@ -50,7 +50,10 @@ class Mlp(nn.Module):
         self.fc2 = nn.Linear(hidden, dim)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.fc2(F.gelu(self.fc1(x)))
+        h = self.fc1(x)
+        if getattr(self.fc2, "supports_pre_gelu", False) and h.dtype == torch.float16:
+            return self.fc2(h, pre_gelu=True)       # GELU fused into fc2's activation quantizer
+        return self.fc2(F.gelu(h))
 
 
 class Block(nn.Module):
@@ -72,7 +75,13 @@ class PatchEmbed(nn.Module):
         self.proj = nn.Conv2d(3, dim, kernel_size=patch, stride=patch)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.proj(x).flatten(2).transpose(1, 2)
+        # Non-overlapping patches: the convolution is a matrix product over flattened patches.  Written that
+        # way (one gather copy + one GEMM) because the library convolution picked for this shape is slow.
+        B, C, H, W = x.shape
+        p = self.proj.kernel_size[0]
+        gh, gw = H // p, W // p
+        patches = x.reshape(B, C, gh, p, gw, p).permute(0, 2, 4, 1, 3, 5).reshape(B, gh * gw, C * p * p)
+        return F.linear(patches, self.proj.weight.reshape(self.proj.out_channels, -1), self.proj.bias)
 
 
 class VisionTransformer(nn.Module):

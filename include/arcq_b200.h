@@ -91,6 +91,19 @@ int arcq_act_quant(const void* x, int x_dtype, int64_t M, int64_t K,
                    void* xhat_out, int xhat_dtype, void* stream);
 
 /*
+ * GELU followed by the activation quantizer above, in one pass: the input is the pre-activation
+ * (fp16 only), each element becomes 0.5*x*(1+erf(x/sqrt 2)) computed in fp32 and rounded to fp16 --
+ * the tensor a separate GELU kernel would have written -- and is then quantised exactly as in
+ * arcq_act_quant.  Fuses the F.gelu between fc1 and fc2 of the reference's MLP block (timm Mlp, called
+ * from the model the reference builds in FQ/fair_qat/timm_quant_models.py:163-167) into step 2 of
+ * ARCQPackedLinearOnTheFly.forward (FQ/fair_qat/arcq_packed_on_the_fly.py:143-145).  Same arguments.
+ */
+int arcq_gelu_act_quant(const void* x, int x_dtype, int64_t M, int64_t K,
+                        const float* thresholds, const float* codebook, int bits, int group_size,
+                        uint8_t* packed_out, float* mu_out, float* sigma_out, float* codesum_out,
+                        void* xhat_out, int xhat_dtype, void* stream);
+
+/*
  * Packed linear:  y[m,n] = bias[n] + sum_k A^[m,k] * W^[n,k]  with both operands
  * reconstructed from packed codes, A^ = mu_a + sigma_a*(cbA[ca] - Sa/gs) and
  * likewise W^, contracted on the tensor cores in fp16 with fp32 accumulation.

@@ -331,3 +331,26 @@ def test_packed_weight_gemm_full_size_properties(pkg, cuda_device):
         _report("packed_weight_gemm_full_size", M=M, K=K, N=N, max_abs_over_rms=err)
         assert err < 5e-3                                                       # only W^ rounding to fp16 differs
         assert pkg.ops.device_status() == 0
+
+
+def test_gelu_fused_into_the_quantizer(pkg, oracle, cuda_device):
+    # small input (8-lane kernel) and large input (one-thread-per-group kernel)
+    for M, K in [(197, 1536), (40 * 197, 1536)]:
+        gen = torch.Generator().manual_seed(M)
+        pre = (torch.randn(M, K, generator=gen) * 1.5).half().to(cuda_device)
+        cb = torch.linspace(-2.6, 2.6, 16, device=cuda_device)
+        th = (cb[:-1] + cb[1:]) / 2
+        act = torch.nn.functional.gelu(pre)                       # what the separate kernel would store (fp16)
+        want = pkg.ops.quantize_activation(act, th, cb, 4, 64)
+        got = pkg.ops.quantize_activation(pre, th, cb, 4, 64, True, True)
+        # the fused GELU is rounded to fp16 like the stored tensor; allow the rare 1-ulp erf difference
+        same = float((want[0] == got[0]).float().mean())
+        assert same > 0.9999, same
+        if M == 197:
+            a = act.float().cpu().numpy()
+            codes, mu, sg, cs = oracle.quantize(a, th.cpu().numpy(), cb.cpu().numpy(), 64)
+            assert (pkg.ops.unpack_codes_u8(got[0], 4, K).cpu().numpy() == codes).mean() > 0.9999
+        xh_want = pkg.ops.quantize_activation_dequant(act, th, cb, 4, 64, torch.float16)
+        xh_got = pkg.ops.quantize_activation_dequant(pre, th, cb, 4, 64, torch.float16, True)
+        assert float((xh_want == xh_got).float().mean()) > 0.999
+    assert pkg.ops.device_status() == 0
