@@ -70,7 +70,7 @@ __host__ __device__ inline WsSmem ws_smem_layout(int bn, int ws, int sa, int bit
   s.raw = s.stage + kEpiStageBytes;
   const uint32_t raw_slot = static_cast<uint32_t>(bn) * raw_row_bytes(bits) + 16;  // +16: 3-bit reads may look 3 bytes ahead
   s.misc = s.raw + kRawSlots * ((raw_slot + 127) & ~127u);
-  s.total = s.misc + 16 * 4 /*lut*/ + 256 * 4 /*bias*/ + 64 * 8 /*barriers*/ + 16;
+  s.total = s.misc + 16 * 4 /*lut*/ + 256 * 4 /*bias*/ + 64 * 8 /*barriers*/ + 16 + 256 * 4 /*pair lut*/;
   return s;
 }
 
@@ -100,6 +100,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   uint64_t* const acc_empty = bars + 54;     // [2]
   uint64_t* const stats_full = bars + 56;    // [1]
   uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(bars + 64);
+  uint32_t* const s_lut2 = s_tmem + 4;          // [256] half2: codebook values of (low nibble, high nibble)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bn = p.bn, G = p.G;
@@ -121,6 +122,11 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   const bool stats_smem = stationary && static_cast<uint32_t>(bn) * G * 12u <= kEpiStageBytes;
 
   if (tid < 16) s_lut[tid] = (tid < (1 << BITS)) ? p.cb_w[tid] : 0.0f;
+  if (tid < 256) {
+    const int lo = tid & 15, hi = tid >> 4;
+    __half2 v = __floats2half2_rn(lo < (1 << BITS) ? p.cb_w[lo] : 0.0f, hi < (1 << BITS) ? p.cb_w[hi] : 0.0f);
+    s_lut2[tid] = *reinterpret_cast<uint32_t*>(&v);
+  }
   for (int i = tid; i < bn; i += kWsThreads) s_bias[i] = (p.bias != nullptr) ? p.bias[n0 + i] : 0.0f;
   if (tid == 0) {
     for (int i = 0; i < p.sa; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
@@ -214,16 +220,15 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
         stamp(8 + 2 * (b0 / nbb));
         for (int g = 0; g < G && ok; ++g) {
           if (stationary) { w_slot = g; w_addr = w_base + g * w_step; }
-          ok = mbar_wait(&w_full[w_slot], stationary ? 0u : w_ph);
+          ok = mbar_wait_spin(&w_full[w_slot], stationary ? 0u : w_ph);
           if (!ok) break;
           const uint64_t db = desc_hi | w_addr;
           for (int j = 0; j < nb; ++j) {
-            ok = mbar_wait(&a_full[a_slot], a_ph);
+            if (p.debug_skip_mma != 7) ok = mbar_wait_spin(&a_full[a_slot], a_ph);   // 7: experiment, no operand wait
             if (!ok) break;
-            tc_fence_after_sync();
             const uint64_t da = desc_hi | a_addr;
             const uint32_t d = tmem_base + ((buf0 + j) & 1) * 256;
-            if (!p.debug_skip_mma) {
+            if (p.debug_skip_mma != 1) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) umma_f16(d, da + 2 * k, db + 2 * k, idesc, (g > 0 || k > 0) ? 1u : 0u);
               umma_commit(&a_empty[a_slot]);
@@ -383,7 +388,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
         if (!ok) break;
         const uint8_t* const raw = sRaw + rslot * raw_slot_bytes + (g & 1) * (8 * BITS);
         uint8_t* const dstw = sW + wslot * bn * 128;
-#pragma unroll 2
+#pragma unroll 3
         for (int i = 0; i < units; ++i) {
           const int r = (ptid >> 3) + 32 * i;
           const uint8_t* rp = raw + r * raw_row_bytes(BITS);
@@ -404,7 +409,19 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
             const long long si = static_cast<long long>(n0 + r) * G + g;
             sigma = __ldg(p.sg_w + si); mu = __ldg(p.mu_w + si); cs = __ldg(p.cs_w + si);
           }
-          rebuild_store8(w, sigma, fmaf(-sigma, cs * (1.0f / 64.0f), mu), s_lut, dstw + sw128_offset(r, chunk));
+          // mu' + sigma * cb[code] for two codes at a time: one look-up in the 256-entry pair table per byte
+          // of nibbles, one half2 fused multiply-add.  (The rebuild is bound by shared-memory accesses --
+          // about 19 per 256 values -- not by arithmetic.)
+          const __half2 s2 = __float2half2_rn(sigma);
+          const __half2 m2 = __float2half2_rn(fmaf(-sigma, cs * (1.0f / 64.0f), mu));
+          uint32_t h[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t pv = s_lut2[(w >> (8 * q)) & 0xFFu];
+            const __half2 r2 = __hfma2(s2, *reinterpret_cast<const __half2*>(&pv), m2);
+            h[q] = *reinterpret_cast<const uint32_t*>(&r2);
+          }
+          *reinterpret_cast<uint4*>(dstw + sw128_offset(r, chunk)) = make_uint4(h[0], h[1], h[2], h[3]);
         }
         fence_proxy_async_smem();
         __syncwarp();

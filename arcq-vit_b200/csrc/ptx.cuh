@@ -68,6 +68,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
   return false;
 }
+// Non-blocking test of a phase (never suspends the thread): for the one thread whose reaction time is on
+// the critical path.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (kMaxPolls << 4); ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+  }
+  return false;
+}
 // Same, for waits that are expected to last: sleeps between polls so that the waiting warps do not
 // take issue slots from the warps that do the work (a poll every ~`ns` nanoseconds).
 __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t ns = 64) {
