@@ -1,0 +1,97 @@
+// Residual add + LayerNorm in one pass over fp16 rows (the glue between the packed linears of a block):
+//   s = fp16(x + y)   (written out when y is given: the updated residual stream)
+//   h = fp16((s - mean(s)) * rsqrt(var(s) + eps) * gamma + beta)
+// One warp per row, 16-byte loads/stores, statistics in fp32 with a two-pass (mean, then centred sum of
+// squares) over values held in registers.  HBM-bound: reads x (and y), writes h (and s) once.
+#pragma once
+#include <cuda_fp16.h>
+#include "ptx.cuh"
+
+namespace arcq {
+
+constexpr int kLnMaxChunks = 8;  // 16-byte chunks per lane: rows up to 32 * 8 * 8 = 2048 values
+
+__global__ void __launch_bounds__(256) add_layernorm_kernel(const __half* __restrict__ x, const __half* __restrict__ y,
+                                                            const float* __restrict__ gamma,
+                                                            const float* __restrict__ beta, float eps, long long M, int K,
+                                                            __half* __restrict__ sum_out, __half* __restrict__ h_out) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const int chunks = K >> 3;
+  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < M; row += warps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * K);
+    const uint4* yr = (y != nullptr) ? reinterpret_cast<const uint4*>(y + row * K) : nullptr;
+    float v[kLnMaxChunks][8];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kLnMaxChunks; ++i) {
+      const int c = lane + 32 * i;
+      if (c < chunks) {
+        const uint4 a = __ldg(xr + c);
+        const __half2* ah = reinterpret_cast<const __half2*>(&a);
+        if (yr != nullptr) {
+          const uint4 b = __ldg(yr + c);
+          const __half2* bh = reinterpret_cast<const __half2*>(&b);
+          uint4 so;
+          __half2* sh = reinterpret_cast<__half2*>(&so);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 fa = __half22float2(ah[j]), fb = __half22float2(bh[j]);
+            sh[j] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);   // the fp16 sum a separate add would store
+            const float2 fs = __half22float2(sh[j]);
+            v[i][2 * j] = fs.x;
+            v[i][2 * j + 1] = fs.y;
+          }
+          if (sum_out != nullptr) reinterpret_cast<uint4*>(sum_out + row * K)[c] = so;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 fa = __half22float2(ah[j]);
+            v[i][2 * j] = fa.x;
+            v[i][2 * j + 1] = fa.y;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum += v[i][j];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum / static_cast<float>(K);
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kLnMaxChunks; ++i) {
+      if (lane + 32 * i < chunks) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = v[i][j] - mean;
+          sq += d * d;
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float rstd = rsqrtf(sq / static_cast<float>(K) + eps);
+#pragma unroll
+    for (int i = 0; i < kLnMaxChunks; ++i) {
+      const int c = lane + 32 * i;
+      if (c < chunks) {
+        const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * c);
+        const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * c + 1);
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta) + 2 * c);
+        const float4 b1 = __ldg(reinterpret_cast<const float4*>(beta) + 2 * c + 1);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          oh[j] = __floats2half2_rn((v[i][2 * j] - mean) * rstd * gg[2 * j] + bb[2 * j],
+                                    (v[i][2 * j + 1] - mean) * rstd * gg[2 * j + 1] + bb[2 * j + 1]);
+        reinterpret_cast<uint4*>(h_out + row * K)[c] = o;
+      }
+    }
+  }
+}
+
+}  // namespace arcq

@@ -15,6 +15,7 @@
 #include "codes.cuh"
 #include "packed_gemm.cuh"
 #include "gemm_ws.cuh"
+#include "add_layernorm.cuh"
 #include <cudaTypedefs.h>
 
 namespace {
@@ -448,6 +449,26 @@ int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const flo
   else ARCQ_LAUNCH_WS(2);
 #undef ARCQ_LAUNCH_WS
   if (e != cudaSuccess) return cuda_fail(e, "packed_weight_gemm launch");
+  return ARCQ_OK;
+}
+
+int arcq_add_layernorm(const void* x, const void* y, const float* gamma, const float* beta, float eps, int64_t M,
+                       int64_t K, void* sum_out, void* h_out, void* stream) {
+  if (x == nullptr || gamma == nullptr || beta == nullptr || h_out == nullptr)
+    return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (M < 0 || K <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape M=%lld K=%lld", (long long)M, (long long)K);
+  if (K % 8 != 0) return fail(ARCQ_E_BAD_SHAPE, "K=%lld must be a multiple of 8", (long long)K);
+  if (K > 32 * 8 * arcq::kLnMaxChunks) return fail(ARCQ_E_TOO_LARGE, "rows longer than %d values are not built", 32 * 8 * arcq::kLnMaxChunks);
+  if (!aligned(x, 16) || !aligned(h_out, 16) || (y != nullptr && !aligned(y, 16)) ||
+      (sum_out != nullptr && !aligned(sum_out, 16)) || !aligned(gamma, 16) || !aligned(beta, 16))
+    return fail(ARCQ_E_ALIGN, "all buffers must be 16-byte aligned");
+  if (M == 0) return ARCQ_OK;
+  const int grid = grid_for(M, 8, 8);
+  arcq::add_layernorm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(x), static_cast<const __half*>(y), gamma, beta, eps, M, static_cast<int>(K),
+      static_cast<__half*>(sum_out), static_cast<__half*>(h_out));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "add_layernorm launch");
   return ARCQ_OK;
 }
 

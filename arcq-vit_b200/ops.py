@@ -175,6 +175,27 @@ def packed_weight_gemm(xhat: torch.Tensor, packed_w, w_center, w_scale, w_code_s
     return y
 
 
+def add_layernorm(x: torch.Tensor, y, norm: torch.nn.LayerNorm):
+    """(x + y, LayerNorm(x + y)) for fp16 CUDA tensors in one kernel; with ``y is None``: (x, LayerNorm(x)).
+    The sum is rounded to fp16 before it is normalised, as the separate add + LayerNorm would do."""
+    lib = _cabi.load()
+    shape = x.shape
+    K = shape[-1]
+    x2 = _dev(x.reshape(-1, K), "x", torch.float16)
+    y2 = None if y is None else _dev(y.reshape(-1, K), "y", torch.float16)
+    if not hasattr(norm, "_arcq_f32"):          # fp32 copies of the affine parameters, made once
+        norm._arcq_f32 = (norm.weight.detach().float().contiguous(), norm.bias.detach().float().contiguous())
+    g32, b32 = norm._arcq_f32
+    h = torch.empty_like(x2)
+    s_out = torch.empty_like(x2) if y2 is not None else None
+    if x2.shape[0] > 0:
+        rc = lib.arcq_add_layernorm(x2.data_ptr(), y2.data_ptr() if y2 is not None else None, g32.data_ptr(),
+                                    b32.data_ptr(), float(norm.eps), x2.shape[0], K,
+                                    s_out.data_ptr() if s_out is not None else None, h.data_ptr(), _stream())
+        _check(rc, "arcq_add_layernorm")
+    return (x if s_out is None else s_out.reshape(shape)), h.reshape(shape)
+
+
 def unpack_codes_u8(packed: torch.Tensor, bits: int, length: int) -> torch.Tensor:
     """uint8 [R, ceil(length*bits/8)] -> uint8 [R, length] (reference: arcq_pack_kernel.cu:136-157)."""
     lib = _cabi.load()

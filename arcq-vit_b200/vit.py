@@ -100,9 +100,24 @@ class VisionTransformer(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x = self.patch_embed(x)
         x = torch.cat([self.cls_token.expand(x.shape[0], -1, -1), x], dim=1) + self.pos_embed
+        if x.is_cuda and x.dtype == torch.float16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 2048:
+            return self._forward_fused_glue(x)
         for blk in self.blocks:
             x = blk(x)
         return self.head(self.norm(x)[:, 0])
+
+    def _forward_fused_glue(self, x: torch.Tensor) -> torch.Tensor:
+        """Same computation as the loop over blocks, with every residual add merged into the LayerNorm
+        that follows it (one kernel instead of two): x += attn(norm1(x)); x += mlp(norm2(x))."""
+        from . import ops
+        _, h = ops.add_layernorm(x, None, self.blocks[0].norm1)
+        n = len(self.blocks)
+        for i, blk in enumerate(self.blocks):
+            a = blk.attn(h)
+            x, h = ops.add_layernorm(x, a, blk.norm2)
+            m = blk.mlp(h)
+            x, h = ops.add_layernorm(x, m, self.blocks[i + 1].norm1 if i + 1 < n else self.norm)
+        return self.head(h[:, 0])
 
 
 def create_vit(name: str, seed: int = 0, num_classes: int = 1000) -> VisionTransformer:

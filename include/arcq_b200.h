@@ -142,6 +142,18 @@ int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const flo
                             void* y, int y_dtype, void* stream);
 
 /*
+ * Residual add + LayerNorm over fp16 rows, the glue between the packed linears of a transformer block:
+ *   s = fp16(x + y), written to sum_out (y and sum_out may both be NULL: plain LayerNorm of x);
+ *   h = fp16((s - mean) * rsqrt(var + eps) * gamma + beta), statistics in fp32, biased variance.
+ * Stands in for the `x = x + branch(...)` add and the following norm1 / norm2 / final norm of the timm
+ * block the reference runs around its packed linears (model built in FQ/fair_qat/timm_quant_models.py:163-167);
+ * the reference has no kernel of its own for it.  x, y, sum_out, h_out: fp16 [M,K]; gamma, beta: fp32 [K];
+ * K % 8 == 0, K <= 2048; all pointers 16-byte aligned.
+ */
+int arcq_add_layernorm(const void* x, const void* y, const float* gamma, const float* beta, float eps,
+                       int64_t M, int64_t K, void* sum_out, void* h_out, void* stream);
+
+/*
  * Unpack codes to one byte per code.  Replaces unpack_codes_u8_cuda,
  * EXT/arcq_pack_kernel.cu:136-157 (kernel :74-90); the int64 variant
  * unpack_codes_cuda (:113-134) is this plus a widening on the host side.

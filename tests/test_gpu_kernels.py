@@ -354,3 +354,30 @@ def test_gelu_fused_into_the_quantizer(pkg, oracle, cuda_device):
         xh_got = pkg.ops.quantize_activation_dequant(pre, th, cb, 4, 64, torch.float16, True)
         assert float((xh_want == xh_got).float().mean()) > 0.999
     assert pkg.ops.device_status() == 0
+
+
+@pytest.mark.parametrize("M,K", [(1, 192), (197, 384), (64 * 197, 384), (1000, 768), (33, 2048)])
+def test_add_layernorm_matches_torch(pkg, cuda_device, M, K):
+    gen = torch.Generator().manual_seed(M + K)
+    x = (torch.randn(M, K, generator=gen) * 2 + 0.5).half().to(cuda_device)
+    y = torch.randn(M, K, generator=gen).half().to(cuda_device)
+    ln = torch.nn.LayerNorm(K, eps=1e-6).to(cuda_device)
+    with torch.no_grad():
+        ln.weight.copy_(1 + 0.1 * torch.randn(K, generator=gen))
+        ln.bias.copy_(0.1 * torch.randn(K, generator=gen))
+    ln = ln.half()
+    with torch.no_grad():
+        s_ref = x + y
+        h_ref = ln(s_ref)
+        s, h = pkg.ops.add_layernorm(x, y, ln)
+        assert torch.equal(s, s_ref)                                   # fp16 sum, same rounding
+        # fp32 reference of the normalisation on the same fp16 sum; the result may differ from torch's by
+        # one fp16 unit in the last place where the two fp32 evaluations round differently
+        f = torch.nn.functional.layer_norm(s_ref.float(), (K,), ln.weight.float(), ln.bias.float(), 1e-6)
+        assert float((h.float() - f).abs().max()) <= 2e-3 * max(1.0, float(f.abs().max()))
+        assert float((h == h_ref).float().mean()) > 0.99
+        x0, h0 = pkg.ops.add_layernorm(x, None, ln)
+        assert x0 is x and float((h0 == ln(x)).float().mean()) > 0.99
+    with pytest.raises(RuntimeError):
+        pkg.ops.add_layernorm(torch.zeros(2, 12, dtype=torch.float16, device=cuda_device), None,
+                              torch.nn.LayerNorm(12).half().to(cuda_device))
