@@ -67,7 +67,7 @@ template <> struct Aq2Row<__half> { static constexpr int kBytes = 128, kPitch = 
 template <> struct Aq2Row<__nv_bfloat16> { static constexpr int kBytes = 128, kPitch = 144; };
 
 template <typename T> __host__ __device__ constexpr size_t aq2_smem_bytes() {
-  return 2 * kAq2Threads * Aq2Row<T>::kPitch + 16 * kAq2Threads * 4 + 3 * 16 * 4 + 16;
+  return 2 * kAq2Threads * Aq2Row<T>::kPitch + 16 * kAq2Threads * 4 + 3 * 16 * 4 + 64 * 4 + 16;
 }
 
 // unpack one staged row into 64 floats
@@ -146,6 +146,33 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
 #pragma unroll
   for (int i = 0; i < L - 1; ++i) exact_r = exact_r && (fabsf(__ldg(thresholds + i)) > 1.0e-15f);
   __syncthreads();
+
+  // First guess by a uniform grid.  u = (t - th_first) * 62 / (th_last - th_first) + 1 puts the thresholds
+  // at positions 1..63; cell k = floor(u) clamped to 0..63.  s_guess[k] = number of thresholds that lie
+  // safely below cell k.  If every (slightly widened) cell holds at most one threshold, the code of a value
+  // in cell k is s_guess[k] + (value > that threshold): one table look-up and one exact comparison instead
+  // of a four-step search.  The exact comparison is the same one the search would end with, so the result is
+  // identical; codebooks with two thresholds closer than a cell fall back to the search.
+  int* const s_guess = reinterpret_cast<int*>(s_cb + 16);      // [64] byte offsets into a table column
+  float grid_scale = 0.0f, grid_off = 0.0f;
+  bool use_guess = false;
+  if (L >= 4) {
+    const float th_first = s_th[0], th_last = s_th[L - 2];
+    grid_scale = 62.0f / (th_last - th_first);
+    grid_off = 1.0f - th_first * grid_scale;
+    int cell_ok = 1;
+    if (tid < 64) {
+      int below = 0, inside = 0;
+      for (int i = 0; i < L - 1; ++i) {
+        const float pos = fmaf(s_th[i], grid_scale, grid_off);
+        below += (pos < static_cast<float>(tid) - 0.02f) ? 1 : 0;
+        inside += (pos >= static_cast<float>(tid) - 0.02f && pos <= static_cast<float>(tid) + 1.02f) ? 1 : 0;
+      }
+      s_guess[tid] = below * (kAq2Threads * 4);
+      cell_ok = (inside <= 1) ? 1 : 0;
+    }
+    use_guess = __syncthreads_and(cell_ok) != 0 && exact_r && isfinite(grid_scale);
+  }
 
   const long long tiles = (total_groups + kAq2Threads - 1) / kAq2Threads;
   float* const my_table = s_table + tid;
@@ -239,7 +266,23 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
         words[c] = w;
       }
     };
-    if (exact_r) {
+    if (use_guess) {
+      const float inv = grid_scale * __frcp_rn(scale);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t w = 0;
+#pragma unroll
+        for (int j = 7; j >= 0; --j) {
+          const float r = v[8 * c + j];
+          const unsigned cell = min(__float2uint_rz(fmaf(r, inv, grid_off)), 63u);   // negative -> 0
+          int off = s_guess[cell];
+          off += (r > *reinterpret_cast<const float*>(col + off)) ? kStep : 0;
+          w = (w << 4) | static_cast<uint32_t>(off >> 9);
+          v[8 * c + j] = *reinterpret_cast<const float*>(reinterpret_cast<const char*>(s_cb) + (off >> 7));
+        }
+        words[c] = w;
+      }
+    } else if (exact_r) {
       classify([](float r) { return r; });
     } else {
       classify([scale](float r) { return __fdiv_rn(r, scale); });
@@ -288,7 +331,7 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
       // tensor ops, written back over this thread's staged row and copied out coalesced by the block
       static_assert(!WRITE_XHAT || sizeof(XH) <= sizeof(T), "reconstruction must fit the staged row");
       static_assert(kAq2Threads * 4 == 512, "the code extraction above assumes a 512-byte table step");
-      const float vm = __fdiv_rn(code_sum, 64.0f);
+      const float mean_f = fmaf(-scale, code_sum * (1.0f / 64.0f), mean);
       constexpr int kOutChunks = 64 * sizeof(XH) / 16;   // 16-byte chunks of one output row
       constexpr int kPer = 16 / sizeof(XH);               // values per chunk
 #pragma unroll
@@ -297,8 +340,10 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int e = kPer * c + (kPer / 4) * j;
-          const float f0 = __fadd_rn(mean, __fmul_rn(scale, __fsub_rn(v[e], vm)));
-          const float f1 = (kPer == 8) ? __fadd_rn(mean, __fmul_rn(scale, __fsub_rn(v[e + (kPer == 8 ? 1 : 0)], vm))) : 0.0f;
+          // mean + scale*(cb - vm) evaluated as one fused multiply-add around mean - scale*vm: equal to the
+          // reference's three rounded steps to within an ulp of fp32, far below the rounding of the output type
+          const float f0 = fmaf(scale, v[e], mean_f);
+          const float f1 = (kPer == 8) ? fmaf(scale, v[e + (kPer == 8 ? 1 : 0)], mean_f) : 0.0f;
           o[j] = aq2_pack2<XH>(f0, f1);
         }
         *reinterpret_cast<uint4*>(row + 16 * c) = make_uint4(o[0], o[1], o[2], o[3]);

@@ -381,3 +381,58 @@ def test_add_layernorm_matches_torch(pkg, cuda_device, M, K):
     with pytest.raises(RuntimeError):
         pkg.ops.add_layernorm(torch.zeros(2, 12, dtype=torch.float16, device=cuda_device), None,
                               torch.nn.LayerNorm(12).half().to(cuda_device))
+
+
+@pytest.mark.parametrize("bits", [4, 3, 2])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.bfloat16])
+def test_staged_quantizer_kernel_matches_oracle_and_the_parallel_kernel(pkg, oracle, cuda_device, bits, dtype):
+    """Inputs with >= 37 888 groups take the one-thread-per-group kernel (staged loads, division-free exact
+    threshold test, uniform-grid first guess); smaller ones the 8-lanes-per-group kernel.  Both must give
+    the oracle's codes and statistics bit for bit."""
+    import os
+    M, K = 2048, 1536                                        # 49 152 groups
+    rng = np.random.default_rng(bits * 7 + 1)
+    X = rng.standard_normal((M, K), dtype=np.float32) * rng.uniform(0.05, 6.0, size=(M, 1)).astype(np.float32)
+    X[:, ::29] *= 12.0
+    x = torch.from_numpy(X).to(dtype)
+    Xr = x.float().numpy()
+    L = 2 ** bits
+    if bits == 4:                                             # shape of a fitted codebook: two ramps around zero
+        cb = np.concatenate([-np.linspace(0, 2.6, 8)[1:][::-1], [0.0], np.linspace(0, 2.58, 9)[1:]]).astype(np.float32)
+    else:
+        cb = np.sort(rng.uniform(-2.8, 2.8, L)).astype(np.float32)
+    th = ((cb[:-1] + cb[1:]) / np.float32(2)).astype(np.float32)
+    codes, mu, sg, cs = oracle.quantize(Xr, th, cb, 64)
+    xd = x.to(cuda_device)
+    p, m, s, c = pkg.ops.quantize_activation(xd, _t(th, cuda_device), _t(cb, cuda_device), bits, 64)
+    assert np.array_equal(p.cpu().numpy(), oracle.pack(codes, bits))
+    assert np.array_equal(m.cpu().numpy(), mu) and np.array_equal(s.cpu().numpy(), sg)
+    assert np.array_equal(c.cpu().numpy(), cs)
+    os.environ["ARCQ_ACT_QUANT_V1"] = "1"                    # same input through the other kernel
+    try:
+        p1, m1, s1, c1 = pkg.ops.quantize_activation(xd, _t(th, cuda_device), _t(cb, cuda_device), bits, 64)
+    finally:
+        del os.environ["ARCQ_ACT_QUANT_V1"]
+    assert torch.equal(p, p1) and torch.equal(m, m1) and torch.equal(s, s1) and torch.equal(c, c1)
+    # reconstruction output: one fused multiply-add per value here, three rounded steps in the reference;
+    # equal after rounding to a 16-bit type except for rare last-bit cases
+    xh = pkg.ops.quantize_activation_dequant(xd, _t(th, cuda_device), _t(cb, cuda_device), bits, 64, dtype)
+    want = torch.from_numpy(oracle.dequant(codes, mu, sg, cb, 64)).to(dtype)
+    if dtype == torch.float32:
+        assert float((xh.cpu() - want).abs().max()) <= 4e-6 * float(want.abs().max())
+    else:
+        assert float((xh.cpu() == want).float().mean()) > 0.999
+        assert float((xh.cpu().float() - want.float()).abs().max()) <= 2.0 ** -7 * float(want.float().abs().max())
+    assert pkg.ops.device_status() == 0
+
+
+def test_staged_quantizer_with_close_thresholds_falls_back_to_the_search(pkg, oracle, cuda_device):
+    # two thresholds closer than a grid cell: the first-guess table is not valid, the search must be used
+    cb = np.array([-2.5, -2.0, -1.5, -1.0, -0.6, -0.3, -0.1, 0.0, 0.004, 0.008, 0.3, 0.7, 1.1, 1.6, 2.1, 2.6], np.float32)
+    th = ((cb[:-1] + cb[1:]) / np.float32(2)).astype(np.float32)
+    rng = np.random.default_rng(5)
+    X = (rng.standard_normal((1024, 2560), dtype=np.float32) * 0.8).astype(np.float32)      # 40 960 groups
+    codes, mu, sg, cs = oracle.quantize(X, th, cb, 64)
+    p, m, s, c = pkg.ops.quantize_activation(_t(X, cuda_device), _t(th, cuda_device), _t(cb, cuda_device), 4, 64)
+    assert np.array_equal(p.cpu().numpy(), oracle.pack(codes, 4))
+    assert np.array_equal(c.cpu().numpy(), cs)
