@@ -241,7 +241,9 @@ bool choose_ws_config(long long M, long long N, long long K, int bits, WsConfig*
     if (ws > 16) continue;
     for (int sa = 8; sa >= 2; --sa) {
       if (force_sa > 0 && sa != force_sa) continue;
-      const size_t need = arcq::ws_smem_layout(best_bn, ws, sa, bits).total;
+      const uint32_t fold = stationary ? 0u : static_cast<uint32_t>(best_bn) * G * 4u;
+      if (stationary && static_cast<uint32_t>(best_bn) * G * 4u > arcq::kEpiStageBytes) continue;
+      const size_t need = arcq::ws_smem_layout(best_bn, ws, sa, bits, fold).total;
       if (need <= kSmemBudget) {
         c->ws = ws; c->sa = sa; c->stationary = stationary;
         c->nbb = stationary ? 1 : 2;

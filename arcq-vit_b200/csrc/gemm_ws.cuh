@@ -59,10 +59,13 @@ __host__ __device__ constexpr int raw_row_bytes(int bits) { return 2 * 8 * bits;
 struct WsSmem {
   // offsets from the 1024-aligned base
   uint32_t a, w, stage, raw, misc;
-  uint32_t total;
+  uint32_t total;   // the fold region, if any, is the last fold_bytes of it
 };
 constexpr uint32_t kEpiStageBytes = 4 * 4096;  // 4 epilogue warps x (32 rows x 128 bytes)
-__host__ __device__ inline WsSmem ws_smem_layout(int bn, int ws, int sa, int bits) {
+constexpr int kLutCopies = 8;   // copies of the pair table, one per (lane & 7): fewer bank conflicts on the look-ups
+// `fold_bytes`: room for the slab's folded statistics when they cannot share the epilogue staging area
+// (streaming ring: bn * G * 4; W-stationary: 0).
+__host__ __device__ inline WsSmem ws_smem_layout(int bn, int ws, int sa, int bits, uint32_t fold_bytes = 0) {
   WsSmem s;
   s.a = 0;
   s.w = s.a + static_cast<uint32_t>(sa) * kStageA;
@@ -70,7 +73,7 @@ __host__ __device__ inline WsSmem ws_smem_layout(int bn, int ws, int sa, int bit
   s.raw = s.stage + kEpiStageBytes;
   const uint32_t raw_slot = static_cast<uint32_t>(bn) * raw_row_bytes(bits) + 16;  // +16: 3-bit reads may look 3 bytes ahead
   s.misc = s.raw + kRawSlots * ((raw_slot + 127) & ~127u);
-  s.total = s.misc + 16 * 4 /*lut*/ + 256 * 4 /*bias*/ + 64 * 8 /*barriers*/ + 16 + 256 * 4 /*pair lut*/;
+  s.total = s.misc + 16 * 4 /*lut*/ + 256 * 4 /*bias*/ + 64 * 8 /*barriers*/ + 16 + 256 * 4 * kLutCopies /*pair lut*/ + fold_bytes;
   return s;
 }
 
@@ -81,7 +84,8 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   extern __shared__ uint8_t smem_raw[];
   // round up to 1024 bytes by pointer arithmetic, so the compiler still knows this is shared memory
   uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  const WsSmem L = ws_smem_layout(p.bn, p.ws, p.sa, BITS);
+  const uint32_t fold_bytes = p.stationary ? 0u : static_cast<uint32_t>(p.bn) * p.G * 4u;
+  const WsSmem L = ws_smem_layout(p.bn, p.ws, p.sa, BITS, fold_bytes);
   uint8_t* const sA = smem + L.a;
   uint8_t* const sW = smem + L.w;
   uint8_t* const sRaw = smem + L.raw;
@@ -98,9 +102,12 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   uint64_t* const raw_empty = bars + 50;     // [2]
   uint64_t* const acc_full = bars + 52;      // [2]
   uint64_t* const acc_empty = bars + 54;     // [2]
-  uint64_t* const stats_full = bars + 56;    // [1]
   uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(bars + 64);
-  uint32_t* const s_lut2 = s_tmem + 4;          // [256] half2: codebook values of (low nibble, high nibble)
+  uint32_t* const s_lut2 = s_tmem + 4;          // [256][8] half2: codebook values of (low nibble, high nibble)
+  // folded statistics of the slab, half2 (sigma, mu - sigma*code_sum/64) per (row, group): in the epilogue
+  // staging area while the slab is built once (W-stationary), else in a region of their own
+  uint32_t* const s_fold = p.stationary ? reinterpret_cast<uint32_t*>(smem + L.stage)
+                                        : reinterpret_cast<uint32_t*>(smem + L.total - fold_bytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bn = p.bn, G = p.G;
@@ -117,15 +124,14 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   auto tile_of = [&](int t) { int q = t + rot; if (q >= my_tiles) q -= my_tiles; return rank + q * ctas_in_slab; };
   const int nbb = p.nbb;
   const bool stationary = p.stationary != 0;
-  // W-stationary: the slab's three statistics arrays (bn x G floats each, contiguous in global memory)
-  // are bulk-copied once into the epilogue staging area, which is idle until the first tile is done.
-  const bool stats_smem = stationary && static_cast<uint32_t>(bn) * G * 12u <= kEpiStageBytes;
+  // W-stationary needs the folded statistics (bn x G words) to fit the epilogue staging area
 
   if (tid < 16) s_lut[tid] = (tid < (1 << BITS)) ? p.cb_w[tid] : 0.0f;
   if (tid < 256) {
     const int lo = tid & 15, hi = tid >> 4;
     __half2 v = __floats2half2_rn(lo < (1 << BITS) ? p.cb_w[lo] : 0.0f, hi < (1 << BITS) ? p.cb_w[hi] : 0.0f);
-    s_lut2[tid] = *reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+    for (int c = 0; c < kLutCopies; ++c) s_lut2[tid * kLutCopies + c] = *reinterpret_cast<uint32_t*>(&v);
   }
   for (int i = tid; i < bn; i += kWsThreads) s_bias[i] = (p.bias != nullptr) ? p.bias[n0 + i] : 0.0f;
   if (tid == 0) {
@@ -133,7 +139,6 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
     for (int i = 0; i < p.ws; ++i) { mbar_init(&w_full[i], kWsProducerWarps); mbar_init(&w_empty[i], 1); }
     for (int i = 0; i < kRawSlots; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kWsProducerWarps); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
-    mbar_init(stats_full, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_w);
@@ -165,14 +170,6 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
       uint32_t a_slot = 0, a_ph = 1, r_slot = 0, r_ph = 1;     // "empty" barriers: first pass is free
       const uint32_t sa = p.sa;
       const int raw_x_step = raw_row_bytes(BITS);
-      if (stats_smem && my_tiles > 0) {
-        const uint32_t sb = static_cast<uint32_t>(bn) * G * 4u;
-        const size_t off = static_cast<size_t>(n0) * G;
-        mbar_arrive_expect_tx(stats_full, 3 * sb);
-        bulk_load_1d(sStage, p.mu_w + off, sb, stats_full);
-        bulk_load_1d(sStage + sb, p.sg_w + off, sb, stats_full);
-        bulk_load_1d(sStage + 2 * sb, p.cs_w + off, sb, stats_full);
-      }
       for (int b0 = 0; b0 < my_tiles && ok; b0 += nbb) {
         const int nb = min(nbb, my_tiles - b0);
         for (int g = 0; g < G && ok; ++g) {
@@ -183,7 +180,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
             tma_load_2d(sRaw + r_slot * raw_slot_bytes, &tm_w, &raw_full[r_slot], (g >> 1) * raw_x_step, n0);
             if (++r_slot == kRawSlots) { r_slot = 0; r_ph ^= 1; }
           }
-          for (int j = 0; j < nb; ++j) {
+          for (int j = 0; j < nb && p.debug_skip_mma != 8; ++j) {
             ok = mbar_wait_relaxed(&a_empty[a_slot], a_ph, 32);
             if (!ok) break;
             mbar_arrive_expect_tx(&a_full[a_slot], kStageA);
@@ -224,14 +221,14 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
           if (!ok) break;
           const uint64_t db = desc_hi | w_addr;
           for (int j = 0; j < nb; ++j) {
-            if (p.debug_skip_mma != 7) ok = mbar_wait_spin(&a_full[a_slot], a_ph);   // 7: experiment, no operand wait
+            if (p.debug_skip_mma < 7) ok = mbar_wait_spin(&a_full[a_slot], a_ph);   // 7, 8: experiments, no operand wait
             if (!ok) break;
             const uint64_t da = desc_hi | a_addr;
             const uint32_t d = tmem_base + ((buf0 + j) & 1) * 256;
             if (p.debug_skip_mma != 1) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) umma_f16(d, da + 2 * k, db + 2 * k, idesc, (g > 0 || k > 0) ? 1u : 0u);
-              umma_commit(&a_empty[a_slot]);
+              if (p.debug_skip_mma != 8) umma_commit(&a_empty[a_slot]);
             } else {
               mbar_arrive(&a_empty[a_slot]);
             }
@@ -374,10 +371,16 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
     // (W-stationary), else from global memory (L2 after the first walk of the slab).
     const int chunk = ptid & 7;
     const int units = (bn * 8 + kWsProducerThreads - 1 - ptid) / kWsProducerThreads;
-    const float* const st_mu = reinterpret_cast<const float*>(sStage);
-    const float* const st_sg = st_mu + bn * G;
-    const float* const st_cs = st_sg + bn * G;
-    if (stats_smem && my_tiles > 0) ok = mbar_wait_relaxed(stats_full, 0);
+    // fold the slab's statistics once: (sigma, mu') as one half2 word per (row, group)
+    if (my_tiles > 0) {
+      for (int i = ptid; i < bn * G; i += kWsProducerThreads) {
+        const long long si = static_cast<long long>(n0) * G + i;
+        const float sigma = __ldg(p.sg_w + si);
+        const __half2 f2 = __floats2half2_rn(sigma, fmaf(-sigma, __ldg(p.cs_w + si) * (1.0f / 64.0f), __ldg(p.mu_w + si)));
+        s_fold[i] = *reinterpret_cast<const uint32_t*>(&f2);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kWsProducerThreads) : "memory");   // producer warps only
+    }
     for (int f = 0; f < fills && ok; ++f) {
       if (my_tiles == 0) break;
       for (int g = 0; g < G && ok; ++g) {
@@ -402,22 +405,18 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
           } else {
             w = spread_2_to_nibbles(*reinterpret_cast<const uint16_t*>(rp + 2 * chunk));
           }
-          float sigma, mu, cs;
-          if (stats_smem) {
-            sigma = st_sg[r * G + g]; mu = st_mu[r * G + g]; cs = st_cs[r * G + g];
-          } else {
-            const long long si = static_cast<long long>(n0 + r) * G + g;
-            sigma = __ldg(p.sg_w + si); mu = __ldg(p.mu_w + si); cs = __ldg(p.cs_w + si);
-          }
-          // mu' + sigma * cb[code] for two codes at a time: one look-up in the 256-entry pair table per byte
-          // of nibbles, one half2 fused multiply-add.  (The rebuild is bound by shared-memory accesses --
-          // about 19 per 256 values -- not by arithmetic.)
-          const __half2 s2 = __float2half2_rn(sigma);
-          const __half2 m2 = __float2half2_rn(fmaf(-sigma, cs * (1.0f / 64.0f), mu));
+          // mu' + sigma * cb[code] for two codes at a time: one look-up in the pair table per byte of nibbles,
+          // one half2 fused multiply-add.  (The rebuild is bound by shared-memory accesses, not arithmetic:
+          // one word of codes, one word of folded statistics, four table look-ups and a 16-byte store per
+          // eight values.)
+          const uint32_t fw = s_fold[r * G + g];
+          const __half2 f2 = *reinterpret_cast<const __half2*>(&fw);
+          const __half2 s2 = __low2half2(f2);
+          const __half2 m2 = __high2half2(f2);
           uint32_t h[4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const uint32_t pv = s_lut2[(w >> (8 * q)) & 0xFFu];
+            const uint32_t pv = s_lut2[((w >> (8 * q)) & 0xFFu) * kLutCopies + (lane & (kLutCopies - 1))];
             const __half2 r2 = __hfma2(s2, *reinterpret_cast<const __half2*>(&pv), m2);
             h[q] = *reinterpret_cast<const uint32_t*>(&r2);
           }
