@@ -16,8 +16,10 @@
 // and RD(b*s) = fma_rd(th, s, h*s) because h is a power of two, so h*s is exact.  Each thread builds
 // its group's 15 limits T_i = fma_rd(th_i, s, h_i*s) once (30 instructions for 64 elements) in a
 // private column of a shared-memory table -- column = thread, so any index is conflict free -- and
-// finds each code by a 4-step binary search of r in that column.  Thresholds too close to zero for
-// h*s to be exact switch the kernel to comparing the IEEE quotient against th itself.
+// finds each code by a 4-step binary search of r in that column.  A threshold that is exactly zero has the
+// boundary 2^-150 (half the smallest subnormal; the tie rounds to zero), formed as fmul_rd(s*2^-100, 2^-50);
+// other thresholds too close to zero for h*s to be exact switch the kernel to comparing the IEEE quotient
+// against th itself.
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
@@ -135,16 +137,23 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
     float th = __int_as_float(0x7f800000), h = 0.0f;
     if (tid < L - 1) {
       th = thresholds[tid];
-      const int b = __float_as_int(th);
-      const float up = __int_as_float(th > 0.0f ? b + 1 : b - 1);   // next float toward +inf (th != 0)
-      h = __fmul_rn(__fsub_rn(up, th), 0.5f);
+      if (th == 0.0f) {
+        h = 0x1p-100f;                                                // times 2^-50 below: 2^-150
+      } else {
+        const int b = __float_as_int(th);
+        const float up = __int_as_float(th > 0.0f ? b + 1 : b - 1);   // next float toward +inf
+        h = __fmul_rn(__fsub_rn(up, th), 0.5f);
+      }
     }
     s_th[tid] = th;
     s_h[tid] = h;
     s_cb[tid] = tid < L ? codebook[tid] : 0.0f;
   }
 #pragma unroll
-  for (int i = 0; i < L - 1; ++i) exact_r = exact_r && (fabsf(__ldg(thresholds + i)) > 1.0e-15f);
+  for (int i = 0; i < L - 1; ++i) {
+    const float th = __ldg(thresholds + i);
+    exact_r = exact_r && (th == 0.0f || fabsf(th) > 1.0e-15f);
+  }
   __syncthreads();
 
   // First guess by a uniform grid.  u = (t - th_first) * 62 / (th_last - th_first) + 1 puts the thresholds
@@ -237,7 +246,8 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
       float t = __int_as_float(0x7f800000);
       if (i < L - 1) {
         const float th = s_th[i];
-        t = exact_r ? __fmaf_rd(th, scale, __fmul_rn(s_h[i], scale)) : th;
+        const float hs = __fmul_rd(__fmul_rn(s_h[i], scale), th == 0.0f ? 0x1p-50f : 1.0f);
+        t = exact_r ? __fmaf_rd(th, scale, hs) : th;
       }
       if (i < L) my_table[i * kTableStride] = t;
     }

@@ -241,9 +241,7 @@ bool choose_ws_config(long long M, long long N, long long K, int bits, WsConfig*
     if (ws > 16) continue;
     for (int sa = 8; sa >= 2; --sa) {
       if (force_sa > 0 && sa != force_sa) continue;
-      const uint32_t fold = stationary ? 0u : static_cast<uint32_t>(best_bn) * G * 4u;
-      if (stationary && static_cast<uint32_t>(best_bn) * G * 4u > arcq::kEpiStageBytes) continue;
-      const size_t need = arcq::ws_smem_layout(best_bn, ws, sa, bits, fold).total;
+      const size_t need = arcq::ws_smem_layout(best_bn, ws, sa, bits, G, stationary != 0).total;
       if (need <= kSmemBudget) {
         c->ws = ws; c->sa = sa; c->stationary = stationary;
         c->nbb = stationary ? 1 : 2;
@@ -283,8 +281,8 @@ static int act_quant_impl(int pre, const void* x, int x_dtype, int64_t M, int64_
                           float* sigma_out, float* codesum_out, void* xhat_out, int xhat_dtype, void* stream) {
   if (x == nullptr || thresholds == nullptr || codebook == nullptr) return fail(ARCQ_E_BAD_ARG, "null input pointer");
   if (packed_out == nullptr && xhat_out == nullptr) return fail(ARCQ_E_BAD_ARG, "no output requested");
-  if ((packed_out != nullptr) != (mu_out != nullptr) || (mu_out != nullptr) != (sigma_out != nullptr))
-    return fail(ARCQ_E_BAD_ARG, "packed_out, mu_out and sigma_out go together");
+  if ((mu_out != nullptr) != (sigma_out != nullptr)) return fail(ARCQ_E_BAD_ARG, "mu_out and sigma_out go together");
+  if (packed_out != nullptr && mu_out == nullptr) return fail(ARCQ_E_BAD_ARG, "packed_out needs mu_out and sigma_out");
   if (codesum_out != nullptr && mu_out == nullptr) return fail(ARCQ_E_BAD_ARG, "codesum_out needs mu_out");
   if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
   if (x_dtype < ARCQ_DT_F32 || x_dtype > ARCQ_DT_BF16) return fail(ARCQ_E_BAD_ARG, "bad x_dtype %d", x_dtype);
@@ -427,7 +425,6 @@ int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const flo
   arcq::WsParams p;
   p.tma_store = use_tma_store ? 1 : 0;
   p.rotate = env_int("ARCQ_WS_ROTATE", 1);
-  p.debug_skip_mma = env_int("ARCQ_WS_SKIP_MMA", 0);
   p.mu_w = mu_w; p.sg_w = sigma_w; p.cs_w = codesum_w; p.cb_w = w_codebook; p.bias = bias; p.y = y;
   p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K); p.G = static_cast<int>(K / 64);
   p.bn = cfg.bn; p.ws = cfg.ws; p.sa = cfg.sa; p.nbb = cfg.nbb; p.stationary = cfg.stationary;

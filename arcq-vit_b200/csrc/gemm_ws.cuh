@@ -40,7 +40,6 @@ struct WsParams {
   int nbb;        // tiles per batch (1 or 2)
   int stationary; // 1: ring holds all G sub-tiles, filled once
   int y_f32;
-  int debug_skip_mma;  // experiments only: consume the stages without issuing MMAs
   int rotate;     // 1: slabs walk their tile list from different starting points
   int tma_store;  // 1: epilogue stages 32-row x 128-byte blocks in shared memory and stores them with TMA
   int* status;
@@ -53,27 +52,46 @@ constexpr int kWsProducerThreads = kWsProducerWarps * 32;
 constexpr int kRawSlots = 2;
 constexpr int kStatusWsTimeout = 0x201;
 
-// bytes of packed codes per row for the two groups one raw load brings in
-__host__ __device__ constexpr int raw_row_bytes(int bits) { return 2 * 8 * bits; }
+// One raw load brings in the packed codes of `raw_groups` 64-column groups for every row of the slab: the
+// fewest groups whose bytes per row (8 * bits each) are a multiple of the 16 bytes a TMA box row must be.
+__host__ __device__ constexpr int raw_groups(int bits) { return bits == 3 ? 2 : 1; }
+__host__ __device__ constexpr int raw_row_bytes(int bits) { return raw_groups(bits) * 8 * bits; }
+__host__ __device__ constexpr uint32_t raw_slot_size(int bn, int bits) {
+  return (static_cast<uint32_t>(bn) * raw_row_bytes(bits) + 16 + 127) & ~127u;   // +16: 3-bit reads may look 3 bytes ahead
+}
 
 struct WsSmem {
   // offsets from the 1024-aligned base
-  uint32_t a, w, stage, raw, misc;
-  uint32_t total;   // the fold region, if any, is the last fold_bytes of it
+  uint32_t a, w, stage, raw, fold, misc;
+  uint32_t total;
 };
 constexpr uint32_t kEpiStageBytes = 4 * 4096;  // 4 epilogue warps x (32 rows x 128 bytes)
 constexpr int kLutCopies = 8;   // copies of the pair table, one per (lane & 7): fewer bank conflicts on the look-ups
-// `fold_bytes`: room for the slab's folded statistics when they cannot share the epilogue staging area
-// (streaming ring: bn * G * 4; W-stationary: 0).
-__host__ __device__ inline WsSmem ws_smem_layout(int bn, int ws, int sa, int bits, uint32_t fold_bytes = 0) {
+// A | W^ ring | build + epilogue area | tables and barriers.  The build area holds the raw-code slots and the
+// slab's folded statistics (bn * G words), the epilogue area the output staging blocks.  A W-stationary slab
+// is built once, before the first accumulator is complete, so there the two areas share their bytes; a
+// streaming ring keeps rebuilding while the epilogue runs and gets both.
+__host__ __device__ inline WsSmem ws_smem_layout(int bn, int ws, int sa, int bits, int G, bool stationary) {
   WsSmem s;
   s.a = 0;
   s.w = s.a + static_cast<uint32_t>(sa) * kStageA;
-  s.stage = s.w + static_cast<uint32_t>(ws) * bn * 128;
-  s.raw = s.stage + kEpiStageBytes;
-  const uint32_t raw_slot = static_cast<uint32_t>(bn) * raw_row_bytes(bits) + 16;  // +16: 3-bit reads may look 3 bytes ahead
-  s.misc = s.raw + kRawSlots * ((raw_slot + 127) & ~127u);
-  s.total = s.misc + 16 * 4 /*lut*/ + 256 * 4 /*bias*/ + 64 * 8 /*barriers*/ + 16 + 256 * 4 * kLutCopies /*pair lut*/ + fold_bytes;
+  const uint32_t area = s.w + static_cast<uint32_t>(ws) * bn * 128;
+  const uint32_t raw_bytes = kRawSlots * raw_slot_size(bn, bits);
+  const uint32_t fold_bytes = (static_cast<uint32_t>(bn) * G * 4u + 127) & ~127u;
+  uint32_t area_bytes;
+  if (stationary) {
+    s.stage = area;
+    s.raw = area;
+    s.fold = s.raw + raw_bytes;
+    area_bytes = raw_bytes + fold_bytes > kEpiStageBytes ? raw_bytes + fold_bytes : kEpiStageBytes;
+  } else {
+    s.stage = area;
+    s.raw = s.stage + kEpiStageBytes;
+    s.fold = s.raw + raw_bytes;
+    area_bytes = kEpiStageBytes + raw_bytes + fold_bytes;
+  }
+  s.misc = area + area_bytes;
+  s.total = s.misc + 16 * 4 /*lut*/ + 256 * 4 /*bias*/ + 64 * 8 /*barriers*/ + 16 + 256 * 4 * kLutCopies /*pair lut*/;
   return s;
 }
 
@@ -84,13 +102,13 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   extern __shared__ uint8_t smem_raw[];
   // round up to 1024 bytes by pointer arithmetic, so the compiler still knows this is shared memory
   uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  const uint32_t fold_bytes = p.stationary ? 0u : static_cast<uint32_t>(p.bn) * p.G * 4u;
-  const WsSmem L = ws_smem_layout(p.bn, p.ws, p.sa, BITS, fold_bytes);
+  const WsSmem L = ws_smem_layout(p.bn, p.ws, p.sa, BITS, p.G, p.stationary != 0);
   uint8_t* const sA = smem + L.a;
   uint8_t* const sW = smem + L.w;
   uint8_t* const sRaw = smem + L.raw;
   uint8_t* const sStage = smem + L.stage;
-  const uint32_t raw_slot_bytes = (static_cast<uint32_t>(p.bn) * raw_row_bytes(BITS) + 16 + 127) & ~127u;
+  const uint32_t raw_slot_bytes = raw_slot_size(p.bn, BITS);
+  constexpr int RG = raw_groups(BITS);
   float* const s_lut = reinterpret_cast<float*>(smem + L.misc);
   float* const s_bias = s_lut + 16;
   uint64_t* const bars = reinterpret_cast<uint64_t*>(s_bias + 256);
@@ -104,10 +122,8 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   uint64_t* const acc_empty = bars + 54;     // [2]
   uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(bars + 64);
   uint32_t* const s_lut2 = s_tmem + 4;          // [256][8] half2: codebook values of (low nibble, high nibble)
-  // folded statistics of the slab, half2 (sigma, mu - sigma*code_sum/64) per (row, group): in the epilogue
-  // staging area while the slab is built once (W-stationary), else in a region of their own
-  uint32_t* const s_fold = p.stationary ? reinterpret_cast<uint32_t*>(smem + L.stage)
-                                        : reinterpret_cast<uint32_t*>(smem + L.total - fold_bytes);
+  // folded statistics of the slab: half2 (sigma, mu - sigma*code_sum/64) per (row, group)
+  uint32_t* const s_fold = reinterpret_cast<uint32_t*>(smem + L.fold);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bn = p.bn, G = p.G;
@@ -124,7 +140,6 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   auto tile_of = [&](int t) { int q = t + rot; if (q >= my_tiles) q -= my_tiles; return rank + q * ctas_in_slab; };
   const int nbb = p.nbb;
   const bool stationary = p.stationary != 0;
-  // W-stationary needs the folded statistics (bn x G words) to fit the epilogue staging area
 
   if (tid < 16) s_lut[tid] = (tid < (1 << BITS)) ? p.cb_w[tid] : 0.0f;
   if (tid < 256) {
@@ -165,89 +180,130 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA issuer
-    if (lane == 0) {
-      // ring positions are advanced incrementally (no division in the loop): slot index + phase bit
-      uint32_t a_slot = 0, a_ph = 1, r_slot = 0, r_ph = 1;     // "empty" barriers: first pass is free
-      const uint32_t sa = p.sa;
-      const int raw_x_step = raw_row_bytes(BITS);
-      for (int b0 = 0; b0 < my_tiles && ok; b0 += nbb) {
-        const int nb = min(nbb, my_tiles - b0);
-        for (int g = 0; g < G && ok; ++g) {
-          if ((!stationary || b0 == 0) && (g & 1) == 0) {
-            ok = mbar_wait_relaxed(&raw_empty[r_slot], r_ph);
-            if (!ok) break;
+    // The whole warp walks the loop and waits (converged code is far cheaper to run than a lone lane in a
+    // divergent branch); lane 0 arms the barriers and issues the copies.
+    uint32_t a_slot = 0, a_ph = 1, r_slot = 0, r_ph = 1;     // "empty" barriers: first pass is free
+    const uint32_t sa = p.sa;
+    const int raw_x_step = raw_row_bytes(BITS);
+    for (int b0 = 0; b0 < my_tiles; b0 += nbb) {
+      const int nb = min(nbb, my_tiles - b0);
+      for (int g = 0; g < G; ++g) {
+        if ((!stationary || b0 == 0) && (g % RG) == 0) {
+          ok = ok && mbar_wait_relaxed(&raw_empty[r_slot], r_ph);
+          if (lane == 0 && ok) {
             mbar_arrive_expect_tx(&raw_full[r_slot], static_cast<uint32_t>(bn) * raw_row_bytes(BITS));
-            tma_load_2d(sRaw + r_slot * raw_slot_bytes, &tm_w, &raw_full[r_slot], (g >> 1) * raw_x_step, n0);
-            if (++r_slot == kRawSlots) { r_slot = 0; r_ph ^= 1; }
+            tma_load_2d(sRaw + r_slot * raw_slot_bytes, &tm_w, &raw_full[r_slot], (g / RG) * raw_x_step, n0);
           }
-          for (int j = 0; j < nb && p.debug_skip_mma != 8; ++j) {
-            ok = mbar_wait_relaxed(&a_empty[a_slot], a_ph, 32);
-            if (!ok) break;
+          __syncwarp();
+          const bool wrap = r_slot + 1 == kRawSlots;
+          r_slot = wrap ? 0u : r_slot + 1;
+          r_ph ^= wrap ? 1u : 0u;
+        }
+        for (int j = 0; j < nb; ++j) {
+          ok = ok && mbar_wait_relaxed(&a_empty[a_slot], a_ph, 32);
+          if (lane == 0 && ok) {
             mbar_arrive_expect_tx(&a_full[a_slot], kStageA);
             tma_load_2d(sA + a_slot * kStageA, &tm_a, &a_full[a_slot], g * 64, tile_of(b0 + j) * kTileM);
-            if (++a_slot == sa) { a_slot = 0; a_ph ^= 1; }
           }
+          __syncwarp();
+          const bool wrap = a_slot + 1 == sa;
+          a_slot = wrap ? 0u : a_slot + 1;
+          a_ph ^= wrap ? 1u : 0u;
         }
       }
+    }
+    if (lane == 0) {
       stamp(1);
       if (!ok) atomicExch(p.status, kStatusWsTimeout);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(kTileM, bn);
-      // ring positions advance incrementally; descriptors are a constant high part plus (address >> 4)
-      const uint64_t desc_hi = umma_desc_sw128(0);
-      const uint32_t sa = p.sa, wsn = p.ws;
-      const uint32_t a_base = smem_u32(sA) >> 4, w_base = smem_u32(sW) >> 4;
-      const uint32_t a_step = kStageA >> 4, w_step = static_cast<uint32_t>(bn) * 128 >> 4;
-      uint32_t a_slot = 0, a_ph = 0, a_addr = a_base;
-      uint32_t w_slot = 0, w_ph = 0, w_addr = w_base;
-      uint32_t acc_ph[2] = {1, 1};      // acc_empty phases: first use of each buffer is free
-      uint32_t buf = 0;                 // accumulator buffer of the next tile
-      for (int b0 = 0; b0 < my_tiles && ok; b0 += nbb) {
-        const int nb = min(nbb, my_tiles - b0);
-        const uint32_t buf0 = buf;
-        for (int j = 0; j < nb && ok; ++j) {
-          const uint32_t bj = (buf0 + j) & 1;
-          ok = mbar_wait_relaxed(&acc_empty[bj], acc_ph[bj], 32);
-          acc_ph[bj] ^= 1;
-        }
-        tc_fence_after_sync();
-        stamp(8 + 2 * (b0 / nbb));
-        for (int g = 0; g < G && ok; ++g) {
-          if (stationary) { w_slot = g; w_addr = w_base + g * w_step; }
-          ok = mbar_wait_spin(&w_full[w_slot], stationary ? 0u : w_ph);
-          if (!ok) break;
-          const uint64_t db = desc_hi | w_addr;
-          for (int j = 0; j < nb; ++j) {
-            if (p.debug_skip_mma < 7) ok = mbar_wait_spin(&a_full[a_slot], a_ph);   // 7, 8: experiments, no operand wait
-            if (!ok) break;
-            const uint64_t da = desc_hi | a_addr;
-            const uint32_t d = tmem_base + ((buf0 + j) & 1) * 256;
-            if (p.debug_skip_mma != 1) {
+    // Same shape: all lanes wait and keep the ring positions, lane 0 issues the MMAs and the commits.
+    const uint32_t idesc = umma_idesc_f16(kTileM, bn);
+    const uint64_t desc_hi = umma_desc_sw128(0);     // descriptors: a constant high part plus (address >> 4)
+    const uint32_t sa = p.sa, wsn = p.ws;
+    const uint32_t a_base = smem_u32(sA) >> 4, w_base = smem_u32(sW) >> 4;
+    const uint32_t a_step = kStageA >> 4, w_step = static_cast<uint32_t>(bn) * 128 >> 4;
+    uint32_t a_slot = 0, a_ph = 0, w_slot = 0, w_ph = 0;
+    uint32_t acc_ph0 = 1, acc_ph1 = 1;   // acc_empty phases: first use of each buffer is free
+    uint32_t buf = 0;                    // accumulator buffer of the next tile
+    int batch = 0;
+    for (int b0 = 0; b0 < my_tiles; b0 += nbb, ++batch) {
+      const int nb = min(nbb, my_tiles - b0);
+      const uint32_t buf0 = buf;
+      for (int j = 0; j < nb; ++j) {
+        const uint32_t bj = (buf0 + j) & 1;
+        ok = ok && mbar_wait_relaxed(&acc_empty[bj], bj ? acc_ph1 : acc_ph0, 32);
+        acc_ph0 ^= bj ? 0u : 1u;
+        acc_ph1 ^= bj ? 1u : 0u;
+      }
+      tc_fence_after_sync();
+      if (lane == 0) stamp(8 + 2 * batch);
+      const bool w_waits = !stationary || b0 == 0;   // a stationary slab is built once
+      const bool st = tr != nullptr && batch == 2 && lane == 0;
+      if (!w_waits && nb == 1) {
+        // steady state of a stationary slab: nothing but "A stage landed -> four MMAs -> free the stage"
+        const uint32_t d = tmem_base + (buf0 & 1) * 256;
+        for (int g = 0; g < G; ++g) {
+          ok = ok && mbar_wait_spin(&a_full[a_slot], a_ph);
+          const uint64_t da = desc_hi | (a_base + a_slot * a_step);
+          const uint64_t db = desc_hi | (w_base + g * w_step);
+          if (lane == 0) {
 #pragma unroll
-              for (int k = 0; k < 4; ++k) umma_f16(d, da + 2 * k, db + 2 * k, idesc, (g > 0 || k > 0) ? 1u : 0u);
-              if (p.debug_skip_mma != 8) umma_commit(&a_empty[a_slot]);
-            } else {
-              mbar_arrive(&a_empty[a_slot]);
+            for (int k = 0; k < 4; ++k) {
+              umma_f16(d, da + 2 * k, db + 2 * k, idesc, (g > 0 || k > 0) ? 1u : 0u);
+              if (st && g < 8) tr[64 + g * 8 + k] = clock64();
             }
-            a_addr += a_step;
-            if (++a_slot == sa) { a_slot = 0; a_addr = a_base; a_ph ^= 1; }
+            umma_commit(&a_empty[a_slot]);
           }
-          if (!stationary) {
-            umma_commit(&w_empty[w_slot]);
-            w_addr += w_step;
-            if (++w_slot == wsn) { w_slot = 0; w_addr = w_base; w_ph ^= 1; }
-          }
+          __syncwarp();
+          const bool wrap = a_slot + 1 == sa;
+          a_slot = wrap ? 0u : a_slot + 1;
+          a_ph ^= wrap ? 1u : 0u;
         }
+      } else
+      for (int g = 0; g < G; ++g) {
+        const uint32_t wi = stationary ? static_cast<uint32_t>(g) : w_slot;
+        if (w_waits) ok = ok && mbar_wait_spin(&w_full[wi], stationary ? 0u : w_ph);
+        if (st && g < 8) tr[64 + g * 8 + 6] = clock64();
+        const uint64_t db = desc_hi | (w_base + wi * w_step);
+        for (int j = 0; j < nb; ++j) {
+          ok = ok && mbar_wait_spin(&a_full[a_slot], a_ph);
+          if (st && g < 8) tr[64 + g * 8 + 7] = clock64();
+          const uint64_t da = desc_hi | (a_base + a_slot * a_step);
+          const uint32_t d = tmem_base + ((buf0 + j) & 1) * 256;
+          if (lane == 0) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              umma_f16(d, da + 2 * k, db + 2 * k, idesc, (g > 0 || k > 0) ? 1u : 0u);
+              if (st && g < 8) tr[64 + g * 8 + k] = clock64();
+            }
+            umma_commit(&a_empty[a_slot]);
+            if (st && g < 8) tr[64 + g * 8 + 4] = clock64();
+          }
+          __syncwarp();
+          const bool wrap = a_slot + 1 == sa;
+          a_slot = wrap ? 0u : a_slot + 1;
+          a_ph ^= wrap ? 1u : 0u;
+          if (st && g < 8) tr[64 + g * 8 + 5] = clock64();
+        }
+        if (!stationary) {
+          if (lane == 0) umma_commit(&w_empty[w_slot]);
+          __syncwarp();
+          const bool wrap = w_slot + 1 == wsn;
+          w_slot = wrap ? 0u : w_slot + 1;
+          w_ph ^= wrap ? 1u : 0u;
+        }
+      }
+      if (lane == 0) {
         if (ok)
           for (int j = 0; j < nb; ++j) umma_commit(&acc_full[(buf0 + j) & 1]);
-        stamp(9 + 2 * (b0 / nbb));
-        buf = (buf0 + nb) & 1;
+        stamp(9 + 2 * batch);
       }
-      if (!ok) atomicExch(p.status, kStatusWsTimeout);
+      __syncwarp();
+      buf = (buf0 + nb) & 1;
     }
+    if (!ok && lane == 0) atomicExch(p.status, kStatusWsTimeout);
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue
     const int lq = warp & 3;  // tensor-memory lane quarter this warp may read
@@ -385,11 +441,11 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
       if (my_tiles == 0) break;
       for (int g = 0; g < G && ok; ++g) {
         const uint32_t rslot = r_slot;
-        if ((g & 1) == 0) ok = mbar_wait_relaxed(&raw_full[rslot], r_ph);
+        if ((g % RG) == 0) ok = mbar_wait_relaxed(&raw_full[rslot], r_ph);
         const uint32_t wslot = stationary ? static_cast<uint32_t>(g) : w_slot;
         if (ok && !stationary) ok = mbar_wait_relaxed(&w_empty[wslot], w_ph);
         if (!ok) break;
-        const uint8_t* const raw = sRaw + rslot * raw_slot_bytes + (g & 1) * (8 * BITS);
+        const uint8_t* const raw = sRaw + rslot * raw_slot_bytes + (g % RG) * (8 * BITS);
         uint8_t* const dstw = sW + wslot * bn * 128;
 #pragma unroll 3
         for (int i = 0; i < units; ++i) {
@@ -426,9 +482,9 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(&w_full[wslot]);
-          if ((g & 1) == 1 || g == G - 1) mbar_arrive(&raw_empty[rslot]);
+          if ((g % RG) == RG - 1 || g == G - 1) mbar_arrive(&raw_empty[rslot]);
         }
-        if ((g & 1) == 1 || g == G - 1) {
+        if ((g % RG) == RG - 1 || g == G - 1) {
           if (++r_slot == kRawSlots) { r_slot = 0; r_ph ^= 1; }
         }
         if (!stationary && ++w_slot == static_cast<uint32_t>(p.ws)) { w_slot = 0; w_ph ^= 1; }

@@ -162,7 +162,11 @@ def kernel_rooflines(pkg, a, dev, pk):
     """Time the two kernels of the packed linear alone on the model's layer shapes (CUDA events on the
     launch stream; rotating buffers so operands and results come from / go to HBM rather than L2)."""
     M, bits = a.batch * TOKENS, a.bits
-    cb = torch.linspace(-2.6, 2.6, 2 ** bits, device=dev)
+    # the shape of a fitted codebook: denser around zero, not symmetric, no threshold exactly at zero
+    half = 2 ** (bits - 1)
+    neg = -torch.linspace(0, 2.6, half + 1)[1:].flip(0) ** 1.15 / 2.6 ** 0.15
+    pos = torch.linspace(0, 2.58, half + 1)[1:half] ** 1.15 / 2.58 ** 0.15
+    cb = torch.cat([neg, torch.tensor([0.02]), pos]).to(dev)
     th = (cb[:-1] + cb[1:]) / 2
     gen = torch.Generator().manual_seed(7)
     reps, rot = a.reps, 4

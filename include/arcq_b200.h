@@ -79,7 +79,7 @@ int arcq_debug_trace(void* device_buffer);
  * reference CPU quantizer's (FQ/quant/dcarcq.py:531-556) bit for bit.
  *   x            [M,K] of x_dtype;  K % group_size == 0;  group_size must be 64
  *   packed_out   uint8 [M, K*bits/8]      (may be NULL when xhat_out is given)
- *   mu_out, sigma_out   fp32 [M, K/64]    (may be NULL together with packed_out)
+ *   mu_out, sigma_out   fp32 [M, K/64]    (both or neither; required with packed_out, optional with xhat_out)
  *   codesum_out  fp32 [M, K/64] or NULL
  *   xhat_out     optional [M,K] of xhat_dtype: the reconstruction
  *                mean + scale*(cb[c] - codesum/64), the output of

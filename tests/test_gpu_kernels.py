@@ -436,3 +436,81 @@ def test_staged_quantizer_with_close_thresholds_falls_back_to_the_search(pkg, or
     p, m, s, c = pkg.ops.quantize_activation(_t(X, cuda_device), _t(th, cuda_device), _t(cb, cuda_device), 4, 64)
     assert np.array_equal(p.cpu().numpy(), oracle.pack(codes, 4))
     assert np.array_equal(c.cpu().numpy(), cs)
+
+
+def _dequant_with_stats(pkg, x, th, cb, bits, pre_gelu=False):
+    """arcq_act_quant through the C ABI with no packed output: reconstruction plus the three statistics."""
+    lib = pkg._cabi.load()
+    M, K = x.shape
+    G = K // 64
+    out = torch.empty_like(x)
+    mu, sg, cs = (torch.empty((M, G), dtype=torch.float32, device=x.device) for _ in range(3))
+    dt = {torch.float32: pkg._cabi.DT_F32, torch.float16: pkg._cabi.DT_F16, torch.bfloat16: pkg._cabi.DT_BF16}[x.dtype]
+    fn = lib.arcq_gelu_act_quant if pre_gelu else lib.arcq_act_quant
+    rc = fn(x.data_ptr(), dt, M, K, th.data_ptr(), cb.data_ptr(), bits, 64, None, mu.data_ptr(), sg.data_ptr(),
+            cs.data_ptr(), out.data_ptr(), dt, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.arcq_last_error_string()
+    return out, mu, sg, cs
+
+
+@pytest.mark.parametrize("bits", [4, 3, 2])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.bfloat16])
+def test_reconstruction_with_statistics_and_no_packed_output(pkg, oracle, cuda_device, bits, dtype):
+    """The call the on-the-fly linear makes, plus the statistics: no packed output.  Statistics must be the
+    oracle's bit for bit through both quantizer kernels, also with a ragged number of groups."""
+    import os
+    M, K = 1021, 2560                                        # 40 840 groups, not a multiple of a block
+    rng = np.random.default_rng(bits * 11 + 3)
+    X = rng.standard_normal((M, K), dtype=np.float32) * rng.uniform(0.05, 6.0, size=(M, 1)).astype(np.float32)
+    X[:, ::31] *= 9.0
+    x = torch.from_numpy(X).to(dtype)
+    L = 2 ** bits
+    if bits == 4:
+        cb = np.concatenate([-np.linspace(0, 2.6, 8)[1:][::-1], [0.0], np.linspace(0, 2.58, 9)[1:]]).astype(np.float32)
+    else:
+        cb = np.sort(rng.uniform(-2.8, 2.8, L)).astype(np.float32)
+    th = ((cb[:-1] + cb[1:]) / np.float32(2)).astype(np.float32)
+    codes, mu, sg, cs = oracle.quantize(x.float().numpy(), th, cb, 64)
+    xd, thd, cbd = x.to(cuda_device), _t(th, cuda_device), _t(cb, cuda_device)
+    xh, m, s, c = _dequant_with_stats(pkg, xd, thd, cbd, bits)
+    assert np.array_equal(m.cpu().numpy(), mu) and np.array_equal(s.cpu().numpy(), sg)
+    assert np.array_equal(c.cpu().numpy(), cs)               # equal code sums <=> equal codes, group by group
+    os.environ["ARCQ_ACT_QUANT_V1"] = "1"                    # same call through the 8-lanes-per-group kernel
+    try:
+        xh1, m1, s1, c1 = _dequant_with_stats(pkg, xd, thd, cbd, bits)
+    finally:
+        os.environ.pop("ARCQ_ACT_QUANT_V1", None)
+    assert torch.equal(c, c1) and torch.equal(m, m1) and torch.equal(s, s1)
+    if dtype == torch.float32:
+        assert float((xh - xh1).abs().max()) <= 4e-6 * float(xh1.abs().max())
+    else:
+        assert float((xh == xh1).float().mean()) > 0.999
+    assert pkg.ops.device_status() == 0
+
+
+def test_quantizer_with_a_threshold_at_zero_and_with_close_thresholds(pkg, oracle, cuda_device):
+    """A threshold that is exactly zero keeps the division-free test (its boundary is half the smallest
+    subnormal); two thresholds closer than a first-guess cell fall back to the search.  GELU fused in front."""
+    rng = np.random.default_rng(17)
+    X = (rng.standard_normal((1024, 2560), dtype=np.float32) * 0.8).astype(np.float32)      # 40 960 groups
+    X[5, :64] = 0.0                                                                          # an all-zero group
+    X[6, :64] = np.float32(1e-30)
+    for cb in (np.array([-2.5, -2.0, -1.5, -1.0, -0.6, -0.3, -0.1, 0.0, 0.004, 0.008, 0.3, 0.7, 1.1, 1.6, 2.1, 2.6], np.float32),
+               np.array([-2.4, -1.9, -1.4, -1.0, -0.7, -0.45, -0.25, -0.1, 0.1, 0.25, 0.45, 0.7, 1.0, 1.4, 1.9, 2.4], np.float32)):
+        th = ((cb[:-1] + cb[1:]) / np.float32(2)).astype(np.float32)      # second codebook: th[7] == 0 exactly
+        codes, mu, sg, cs = oracle.quantize(X, th, cb, 64)
+        xh, m, s, c = _dequant_with_stats(pkg, _t(X, cuda_device), _t(th, cuda_device), _t(cb, cuda_device), 4)
+        assert np.array_equal(c.cpu().numpy(), cs) and np.array_equal(s.cpu().numpy(), sg)
+        p = pkg.ops.quantize_activation(_t(X, cuda_device), _t(th, cuda_device), _t(cb, cuda_device), 4, 64)[0]
+        assert np.array_equal(p.cpu().numpy(), oracle.pack(codes, 4))
+        want = oracle.dequant(codes, mu, sg, cb, 64)
+        assert float(np.abs(xh.cpu().numpy() - want).max()) <= 4e-6 * float(np.abs(want).max())
+    # GELU in front: same as quantising the stored fp16 activation
+    pre = (torch.randn(600, 1536, generator=torch.Generator().manual_seed(3)) * 1.5).half().to(cuda_device)
+    cbt = torch.linspace(-2.6, 2.6, 16, device=cuda_device)
+    tht = (cbt[:-1] + cbt[1:]) / 2
+    act = torch.nn.functional.gelu(pre)
+    want = _dequant_with_stats(pkg, act, tht, cbt, 4)[0]
+    got = _dequant_with_stats(pkg, pre, tht, cbt, 4, pre_gelu=True)[0]
+    assert float((want == got).float().mean()) > 0.999
+    assert pkg.ops.device_status() == 0
