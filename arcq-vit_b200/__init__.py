@@ -7,7 +7,7 @@ from . import _cabi, codebook, ops, packing, sharding  # noqa: F401
 from .convert import (convert_arcq_linear_to_packed, count_packed_linear, load_packed_state_dict,  # noqa: F401
                       to_on_the_fly)
 from .packed_linear import ARCQPackedLinear, ARCQPackedLinearOnTheFly, quantize_weight  # noqa: F401
-from .vit import (DEIT_CONFIGS, GraphedModel, VisionTransformer, create_vit, pack_linear,  # noqa: F401
+from .vit import (DEIT_CONFIGS, GraphedModel, HostPipeline, VisionTransformer, create_vit, pack_linear,  # noqa: F401
                   pack_model_with_codebooks, quantise_model, quantised_linear_names)
 
 __version__ = "0.1.0"

@@ -29,6 +29,7 @@
 namespace arcq {
 
 constexpr int kAq2Threads = 128;
+constexpr int kAq2Cells = 256;   // cells of the uniform first-guess grid over the threshold range
 
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
@@ -69,7 +70,7 @@ template <> struct Aq2Row<__half> { static constexpr int kBytes = 128, kPitch = 
 template <> struct Aq2Row<__nv_bfloat16> { static constexpr int kBytes = 128, kPitch = 144; };
 
 template <typename T> __host__ __device__ constexpr size_t aq2_smem_bytes() {
-  return 2 * kAq2Threads * Aq2Row<T>::kPitch + 16 * kAq2Threads * 4 + 3 * 16 * 4 + 64 * 4 + 16;
+  return 2 * kAq2Threads * Aq2Row<T>::kPitch + 16 * kAq2Threads * 4 + 3 * 16 * 4 + kAq2Cells * 4 + 16;
 }
 
 // unpack one staged row into 64 floats
@@ -107,6 +108,32 @@ template <> __device__ __forceinline__ void aq2_load_row<__nv_bfloat16>(const ui
       x[8 * c + 2 * j + 1] = __uint_as_float(v[j] & 0xFFFF0000u);
     }
   }
+}
+
+// Exact GELU, 0.5*x*(1+erf(x/sqrt 2)) in fp32 rounded to T, for a loop that all 32 lanes of a warp run
+// together.  erf(z) for |z| < 0.9277 is z*P(z*z) with a degree-7 least-squares fit on Chebyshev nodes (max
+// error 1e-11 before rounding); over every fp16 input in that range the rounded GELU differs from the exactly
+// rounded one for 3 inputs of 31 360 -- the library erff gives 2.  Larger arguments call erff, but only when
+// some lane of the warp needs it: the branch is warp-uniform, so the common case (pre-activations of a few
+// units at most) never executes the long path.  Each element's result depends on its own value only.
+template <typename T> __device__ __forceinline__ float gelu_rounded_warp(float x) {
+  const float z = x * 0.70710678118654752440f;
+  const float s = z * z;
+  float r = -1.0267135621688794e-05f;
+  r = fmaf(r, s, 0.00011447568977018818f);
+  r = fmaf(r, s, -0.0008505592122673988f);
+  r = fmaf(r, s, 0.005222289357334375f);
+  r = fmaf(r, s, -0.026865806430578232f);
+  r = fmaf(r, s, 0.11283788084983826f);
+  r = fmaf(r, s, -0.37612637877464294f);
+  r = fmaf(r, s, 1.128379225730896f);
+  float e = z * r;
+  const bool big = !(fabsf(z) < 0.9277f);
+  if (__any_sync(0xffffffffu, big)) {
+    const float el = erff(z);
+    e = big ? el : e;
+  }
+  return round_to<T>(x * 0.5f * (1.0f + e));
 }
 
 // XH: type of the optional reconstruction output (same byte size as T is not required).
@@ -156,29 +183,30 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
   }
   __syncthreads();
 
-  // First guess by a uniform grid.  u = (t - th_first) * 62 / (th_last - th_first) + 1 puts the thresholds
-  // at positions 1..63; cell k = floor(u) clamped to 0..63.  s_guess[k] = number of thresholds that lie
-  // safely below cell k.  If every (slightly widened) cell holds at most one threshold, the code of a value
-  // in cell k is s_guess[k] + (value > that threshold): one table look-up and one exact comparison instead
-  // of a four-step search.  The exact comparison is the same one the search would end with, so the result is
-  // identical; codebooks with two thresholds closer than a cell fall back to the search.
-  int* const s_guess = reinterpret_cast<int*>(s_cb + 16);      // [64] byte offsets into a table column
+  // First guess by a uniform grid.  u = (t - th_first) * (C-2) / (th_last - th_first) + 1 puts the thresholds
+  // at positions 1..C-1; cell k = floor(u) clamped to 0..C-1 (C = kAq2Cells).  s_guess[k] = number of
+  // thresholds that lie safely below cell k.  If every (slightly widened) cell holds at most one threshold,
+  // the code of a value in cell k is s_guess[k] + (value > that threshold): one table look-up and one exact
+  // comparison instead of a four-step search.  The exact comparison is the same one the search would end
+  // with, so the result is identical; codebooks with two thresholds closer than a cell (1/254 of the
+  // threshold range) fall back to the search.
+  int* const s_guess = reinterpret_cast<int*>(s_cb + 16);      // [kAq2Cells] byte offsets into a table column
   float grid_scale = 0.0f, grid_off = 0.0f;
   bool use_guess = false;
   if (L >= 4) {
     const float th_first = s_th[0], th_last = s_th[L - 2];
-    grid_scale = 62.0f / (th_last - th_first);
+    grid_scale = static_cast<float>(kAq2Cells - 2) / (th_last - th_first);
     grid_off = 1.0f - th_first * grid_scale;
     int cell_ok = 1;
-    if (tid < 64) {
+    for (int k = tid; k < kAq2Cells; k += kAq2Threads) {
       int below = 0, inside = 0;
       for (int i = 0; i < L - 1; ++i) {
         const float pos = fmaf(s_th[i], grid_scale, grid_off);
-        below += (pos < static_cast<float>(tid) - 0.02f) ? 1 : 0;
-        inside += (pos >= static_cast<float>(tid) - 0.02f && pos <= static_cast<float>(tid) + 1.02f) ? 1 : 0;
+        below += (pos < static_cast<float>(k) - 0.05f) ? 1 : 0;
+        inside += (pos >= static_cast<float>(k) - 0.05f && pos <= static_cast<float>(k) + 1.05f) ? 1 : 0;
       }
-      s_guess[tid] = below * (kAq2Threads * 4);
-      cell_ok = (inside <= 1) ? 1 : 0;
+      s_guess[k] = below * (kAq2Threads * 4);
+      cell_ok = (inside <= 1) ? cell_ok : 0;
     }
     use_guess = __syncthreads_and(cell_ok) != 0 && exact_r && isfinite(grid_scale);
   }
@@ -219,13 +247,13 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
     float v[64];
     if (valid) {
       aq2_load_row<T>(row, v);
-      if (PRE != 0) {
-#pragma unroll
-        for (int j = 0; j < 64; ++j) v[j] = pre_op<T, PRE>(v[j]);
-      }
     } else {
 #pragma unroll
       for (int j = 0; j < 64; ++j) v[j] = 0.0f;
+    }
+    if (PRE == 1) {   // every lane takes part (idle ones on zeros): the GELU below votes across the warp
+#pragma unroll
+      for (int j = 0; j < 64; ++j) v[j] = gelu_rounded_warp<T>(v[j]);
     }
     const float mean = __fdiv_rn(sum64_ref_order(v), 64.0f);
     float var;
@@ -284,7 +312,8 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
 #pragma unroll
         for (int j = 7; j >= 0; --j) {
           const float r = v[8 * c + j];
-          const unsigned cell = min(__float2uint_rz(fmaf(r, inv, grid_off)), 63u);   // negative -> 0
+          const unsigned cell = min(__float2uint_rz(fmaf(r, inv, grid_off)),
+                                    static_cast<unsigned>(kAq2Cells - 1));             // negative -> 0
           int off = s_guess[cell];
           off += (r > *reinterpret_cast<const float*>(col + off)) ? kStep : 0;
           w = (w << 4) | static_cast<uint32_t>(off >> 9);

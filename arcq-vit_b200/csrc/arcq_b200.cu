@@ -66,7 +66,7 @@ int sm_count() {
 
 // Tuning overrides for experiments (unset in normal use): ARCQ_WS_BN, ARCQ_WS_SA, ARCQ_WS_WS,
 // ARCQ_WS_STATIONARY, ARCQ_WS_NBB, ARCQ_WS_GRID,
-// ARCQ_WS_TMA_STORE, ARCQ_WS_ROTATE, ARCQ_ACT_QUANT_V1.
+// ARCQ_WS_TMA_STORE, ARCQ_WS_ROTATE, ARCQ_ACT_QUANT_V1, ARCQ_LN_PLAIN.
 int env_int(const char* name, int dflt) {
   const char* v = getenv(name);
   return (v != nullptr && *v != 0) ? atoi(v) : dflt;
@@ -206,7 +206,7 @@ constexpr size_t kSmemBudget = 232448 - 1024;
 
 // Pick slab width, ring depths and grid for the warp-specialised GEMM; false if the shape is not
 // one it handles (the caller then reports ARCQ_E_UNSUPPORTED).
-bool choose_ws_config(long long M, long long N, long long K, int bits, WsConfig* c) {
+bool choose_ws_config(long long M, long long N, long long K, int bits, bool dense, WsConfig* c) {
   const int G = static_cast<int>(K / 64);
   const long long tiles_m = (M + arcq::kTileM - 1) / arcq::kTileM;
   const int sms = sm_count();
@@ -236,12 +236,13 @@ bool choose_ws_config(long long M, long long N, long long K, int bits, WsConfig*
   // stationary if all G sub-tiles plus two A stages fit
   for (int stationary = 1; stationary >= 0; --stationary) {
     if (force_stat >= 0 && stationary != force_stat) continue;
-    int ws = stationary ? G : (G < 3 ? G : 3);
+    const int stream_slots = dense ? 4 : 3;
+    int ws = stationary ? G : (G < stream_slots ? G : stream_slots);
     if (!stationary && force_ws > 0 && force_ws <= 16) ws = force_ws;
     if (ws > 16) continue;
     for (int sa = 8; sa >= 2; --sa) {
       if (force_sa > 0 && sa != force_sa) continue;
-      const size_t need = arcq::ws_smem_layout(best_bn, ws, sa, bits, G, stationary != 0).total;
+      const size_t need = arcq::ws_smem_layout(best_bn, ws, sa, bits, G, stationary != 0, dense).total;
       if (need <= kSmemBudget) {
         c->ws = ws; c->sa = sa; c->stationary = stationary;
         c->nbb = stationary ? 1 : 2;
@@ -381,37 +382,27 @@ int arcq_packed_gemm(const uint8_t* packed_x, const float* mu_a, const float* si
 }
 
 
-int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const float* mu_w, const float* sigma_w,
-                            const float* codesum_w, const float* w_codebook, const float* bias, int bits,
-                            int group_size, int64_t M, int64_t N, int64_t K, void* y, int y_dtype, void* stream) {
-  if (!xhat || !packed_w || !mu_w || !sigma_w || !codesum_w || !w_codebook || !y)
-    return fail(ARCQ_E_BAD_ARG, "null pointer argument");
-  if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
-  if (y_dtype != ARCQ_DT_F16 && y_dtype != ARCQ_DT_F32) return fail(ARCQ_E_BAD_ARG, "y_dtype must be f16 or f32");
-  if (M < 0 || N <= 0 || K <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape M=%lld N=%lld K=%lld", (long long)M,
-                                              (long long)N, (long long)K);
-  if (group_size <= 0 || K % group_size != 0)
-    return fail(ARCQ_E_BAD_SHAPE, "K=%lld is not a multiple of group_size=%d", (long long)K, group_size);
-  if (group_size != 64) return fail(ARCQ_E_UNSUPPORTED, "group_size %d: only 64 is built", group_size);
-  if (N % 16 != 0) return fail(ARCQ_E_UNSUPPORTED, "N=%lld: this entry point needs N %% 16 == 0", (long long)N);
-  if ((K * bits / 8) % 16 != 0)
-    return fail(ARCQ_E_UNSUPPORTED, "packed row of %lld bytes is not a multiple of 16 (TMA stride rule)",
-                (long long)(K * bits / 8));
-  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > (1 << 20)) return fail(ARCQ_E_TOO_LARGE, "shape too large");
-  if (!aligned(xhat, 16) || !aligned(packed_w, 16) || !aligned(y, 16))
-    return fail(ARCQ_E_ALIGN, "xhat, packed_w and y must be 16-byte aligned");
-  if (M == 0) return ARCQ_OK;
+// Launch of the persistent GEMM for either weight form: packed codes + statistics (rebuilt in shared
+// memory) or an fp16 matrix (`dense`; mu_w .. w_codebook unused).  Arguments are already validated.
+static int launch_ws_gemm(bool dense, const void* xhat, const void* w, const float* mu_w, const float* sigma_w,
+                          const float* codesum_w, const float* w_codebook, const float* bias, int bits, int64_t M,
+                          int64_t N, int64_t K, void* y, int y_dtype, void* stream) {
   WsConfig cfg;
-  if (!choose_ws_config(M, N, K, bits, &cfg)) return fail(ARCQ_E_UNSUPPORTED, "no tile configuration for this shape");
+  if (!choose_ws_config(M, N, K, bits, dense, &cfg)) return fail(ARCQ_E_UNSUPPORTED, "no tile configuration for this shape");
 
   CUtensorMap tm_a, tm_w;
   if (!make_tensor_map_2d(&tm_a, xhat, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, static_cast<uint64_t>(M),
                           static_cast<uint64_t>(K), 64, arcq::kTileM, CU_TENSOR_MAP_SWIZZLE_128B))
     return fail(ARCQ_E_CUDA, "cuTensorMapEncodeTiled failed for the activation matrix");
-  if (!make_tensor_map_2d(&tm_w, packed_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, static_cast<uint64_t>(N),
-                          static_cast<uint64_t>(K * bits / 8), arcq::raw_row_bytes(bits), cfg.bn,
-                          CU_TENSOR_MAP_SWIZZLE_NONE))
+  if (dense) {
+    if (!make_tensor_map_2d(&tm_w, w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, static_cast<uint64_t>(N),
+                            static_cast<uint64_t>(K), 64, cfg.bn, CU_TENSOR_MAP_SWIZZLE_128B))
+      return fail(ARCQ_E_CUDA, "cuTensorMapEncodeTiled failed for the weight matrix");
+  } else if (!make_tensor_map_2d(&tm_w, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, static_cast<uint64_t>(N),
+                                 static_cast<uint64_t>(K * bits / 8), arcq::raw_row_bytes(bits), cfg.bn,
+                                 CU_TENSOR_MAP_SWIZZLE_NONE)) {
     return fail(ARCQ_E_CUDA, "cuTensorMapEncodeTiled failed for the packed weight");
+  }
 
   // output tensor map for the TMA-store epilogue: 32-row blocks of 64 bytes (32 fp16 / 16 fp32 columns)
   const int out_cw = (y_dtype == ARCQ_DT_F32) ? 16 : 32;
@@ -428,6 +419,7 @@ int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const flo
   p.mu_w = mu_w; p.sg_w = sigma_w; p.cs_w = codesum_w; p.cb_w = w_codebook; p.bias = bias; p.y = y;
   p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K); p.G = static_cast<int>(K / 64);
   p.bn = cfg.bn; p.ws = cfg.ws; p.sa = cfg.sa; p.nbb = cfg.nbb; p.stationary = cfg.stationary;
+  p.dense = dense ? 1 : 0;
   p.y_f32 = (y_dtype == ARCQ_DT_F32) ? 1 : 0;
   p.status = status_ptr();
   p.trace = g_trace_buf;
@@ -451,6 +443,45 @@ int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const flo
   return ARCQ_OK;
 }
 
+int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const float* mu_w, const float* sigma_w,
+                            const float* codesum_w, const float* w_codebook, const float* bias, int bits,
+                            int group_size, int64_t M, int64_t N, int64_t K, void* y, int y_dtype, void* stream) {
+  if (!xhat || !packed_w || !mu_w || !sigma_w || !codesum_w || !w_codebook || !y)
+    return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
+  if (y_dtype != ARCQ_DT_F16 && y_dtype != ARCQ_DT_F32) return fail(ARCQ_E_BAD_ARG, "y_dtype must be f16 or f32");
+  if (M < 0 || N <= 0 || K <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape M=%lld N=%lld K=%lld", (long long)M,
+                                              (long long)N, (long long)K);
+  if (group_size <= 0 || K % group_size != 0)
+    return fail(ARCQ_E_BAD_SHAPE, "K=%lld is not a multiple of group_size=%d", (long long)K, group_size);
+  if (group_size != 64) return fail(ARCQ_E_UNSUPPORTED, "group_size %d: only 64 is built", group_size);
+  if (N % 16 != 0) return fail(ARCQ_E_UNSUPPORTED, "N=%lld: this entry point needs N %% 16 == 0", (long long)N);
+  if ((K * bits / 8) % 16 != 0)
+    return fail(ARCQ_E_UNSUPPORTED, "packed row of %lld bytes is not a multiple of 16 (TMA stride rule)",
+                (long long)(K * bits / 8));
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > (1 << 20)) return fail(ARCQ_E_TOO_LARGE, "shape too large");
+  if (!aligned(xhat, 16) || !aligned(packed_w, 16) || !aligned(y, 16))
+    return fail(ARCQ_E_ALIGN, "xhat, packed_w and y must be 16-byte aligned");
+  if (M == 0) return ARCQ_OK;
+  return launch_ws_gemm(false, xhat, packed_w, mu_w, sigma_w, codesum_w, w_codebook, bias, bits, M, N, K, y, y_dtype,
+                        stream);
+}
+
+int arcq_dense_weight_gemm(const void* xhat, const void* w16, const float* bias, int64_t M, int64_t N, int64_t K,
+                           void* y, int y_dtype, void* stream) {
+  if (!xhat || !w16 || !y) return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (y_dtype != ARCQ_DT_F16 && y_dtype != ARCQ_DT_F32) return fail(ARCQ_E_BAD_ARG, "y_dtype must be f16 or f32");
+  if (M < 0 || N <= 0 || K <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape M=%lld N=%lld K=%lld", (long long)M,
+                                              (long long)N, (long long)K);
+  if (K % 64 != 0) return fail(ARCQ_E_UNSUPPORTED, "K=%lld: this entry point needs K %% 64 == 0", (long long)K);
+  if (N % 16 != 0) return fail(ARCQ_E_UNSUPPORTED, "N=%lld: this entry point needs N %% 16 == 0", (long long)N);
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > (1 << 20)) return fail(ARCQ_E_TOO_LARGE, "shape too large");
+  if (!aligned(xhat, 16) || !aligned(w16, 16) || !aligned(y, 16))
+    return fail(ARCQ_E_ALIGN, "xhat, w16 and y must be 16-byte aligned");
+  if (M == 0) return ARCQ_OK;
+  return launch_ws_gemm(true, xhat, w16, nullptr, nullptr, nullptr, nullptr, bias, 4, M, N, K, y, y_dtype, stream);
+}
+
 int arcq_add_layernorm(const void* x, const void* y, const float* gamma, const float* beta, float eps, int64_t M,
                        int64_t K, void* sum_out, void* h_out, void* stream) {
   if (x == nullptr || gamma == nullptr || beta == nullptr || h_out == nullptr)
@@ -462,10 +493,19 @@ int arcq_add_layernorm(const void* x, const void* y, const float* gamma, const f
       (sum_out != nullptr && !aligned(sum_out, 16)) || !aligned(gamma, 16) || !aligned(beta, 16))
     return fail(ARCQ_E_ALIGN, "all buffers must be 16-byte aligned");
   if (M == 0) return ARCQ_OK;
-  const int grid = grid_for(M, 8, 8);
-  arcq::add_layernorm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(x), static_cast<const __half*>(y), gamma, beta, eps, M, static_cast<int>(K),
-      static_cast<__half*>(sum_out), static_cast<__half*>(h_out));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __half *xh = static_cast<const __half*>(x), *yh = static_cast<const __half*>(y);
+  __half *so = static_cast<__half*>(sum_out), *ho = static_cast<__half*>(h_out);
+  const bool plain = env_int("ARCQ_LN_PLAIN", 0) != 0;
+  if (K == 384 && !plain) {          // 16 lanes per row, 2 rows per warp
+    arcq::add_layernorm_rows_kernel<16><<<grid_for(M, 16, 6), 256, 0, st>>>(xh, yh, gamma, beta, eps, M, so, ho);
+  } else if (K == 192 && !plain) {
+    arcq::add_layernorm_rows_kernel<8><<<grid_for(M, 32, 6), 256, 0, st>>>(xh, yh, gamma, beta, eps, M, so, ho);
+  } else if (K == 768 && !plain) {
+    arcq::add_layernorm_rows_kernel<32><<<grid_for(M, 8, 6), 256, 0, st>>>(xh, yh, gamma, beta, eps, M, so, ho);
+  } else {
+    arcq::add_layernorm_kernel<<<grid_for(M, 8, 8), 256, 0, st>>>(xh, yh, gamma, beta, eps, M, static_cast<int>(K), so, ho);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "add_layernorm launch");
   return ARCQ_OK;

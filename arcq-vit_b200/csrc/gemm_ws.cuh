@@ -39,6 +39,7 @@ struct WsParams {
   int sa;         // A stages
   int nbb;        // tiles per batch (1 or 2)
   int stationary; // 1: ring holds all G sub-tiles, filled once
+  int dense;      // 1: the weight operand is an fp16 matrix [N,K] in global memory (its sub-tiles arrive by TMA, nothing is rebuilt)
   int y_f32;
   int rotate;     // 1: slabs walk their tile list from different starting points
   int tma_store;  // 1: epilogue stages 32-row x 128-byte blocks in shared memory and stores them with TMA
@@ -71,13 +72,14 @@ constexpr int kLutCopies = 8;   // copies of the pair table, one per (lane & 7):
 // slab's folded statistics (bn * G words), the epilogue area the output staging blocks.  A W-stationary slab
 // is built once, before the first accumulator is complete, so there the two areas share their bytes; a
 // streaming ring keeps rebuilding while the epilogue runs and gets both.
-__host__ __device__ inline WsSmem ws_smem_layout(int bn, int ws, int sa, int bits, int G, bool stationary) {
+__host__ __device__ inline WsSmem ws_smem_layout(int bn, int ws, int sa, int bits, int G, bool stationary,
+                                                 bool dense = false) {
   WsSmem s;
   s.a = 0;
   s.w = s.a + static_cast<uint32_t>(sa) * kStageA;
   const uint32_t area = s.w + static_cast<uint32_t>(ws) * bn * 128;
-  const uint32_t raw_bytes = kRawSlots * raw_slot_size(bn, bits);
-  const uint32_t fold_bytes = (static_cast<uint32_t>(bn) * G * 4u + 127) & ~127u;
+  const uint32_t raw_bytes = dense ? 0u : kRawSlots * raw_slot_size(bn, bits);
+  const uint32_t fold_bytes = dense ? 0u : (static_cast<uint32_t>(bn) * G * 4u + 127) & ~127u;
   uint32_t area_bytes;
   if (stationary) {
     s.stage = area;
@@ -102,7 +104,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   extern __shared__ uint8_t smem_raw[];
   // round up to 1024 bytes by pointer arithmetic, so the compiler still knows this is shared memory
   uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  const WsSmem L = ws_smem_layout(p.bn, p.ws, p.sa, BITS, p.G, p.stationary != 0);
+  const WsSmem L = ws_smem_layout(p.bn, p.ws, p.sa, BITS, p.G, p.stationary != 0, p.dense != 0);
   uint8_t* const sA = smem + L.a;
   uint8_t* const sW = smem + L.w;
   uint8_t* const sRaw = smem + L.raw;
@@ -141,8 +143,9 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   const int nbb = p.nbb;
   const bool stationary = p.stationary != 0;
 
-  if (tid < 16) s_lut[tid] = (tid < (1 << BITS)) ? p.cb_w[tid] : 0.0f;
-  if (tid < 256) {
+  const bool dense = p.dense != 0;
+  if (tid < 16 && !dense) s_lut[tid] = (tid < (1 << BITS)) ? p.cb_w[tid] : 0.0f;
+  if (tid < 256 && !dense) {
     const int lo = tid & 15, hi = tid >> 4;
     __half2 v = __floats2half2_rn(lo < (1 << BITS) ? p.cb_w[lo] : 0.0f, hi < (1 << BITS) ? p.cb_w[hi] : 0.0f);
 #pragma unroll
@@ -151,7 +154,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   for (int i = tid; i < bn; i += kWsThreads) s_bias[i] = (p.bias != nullptr) ? p.bias[n0 + i] : 0.0f;
   if (tid == 0) {
     for (int i = 0; i < p.sa; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
-    for (int i = 0; i < p.ws; ++i) { mbar_init(&w_full[i], kWsProducerWarps); mbar_init(&w_empty[i], 1); }
+    for (int i = 0; i < p.ws; ++i) { mbar_init(&w_full[i], dense ? 1 : kWsProducerWarps); mbar_init(&w_empty[i], 1); }
     for (int i = 0; i < kRawSlots; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kWsProducerWarps); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
     mbar_fence_init();
@@ -183,12 +186,28 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
     // The whole warp walks the loop and waits (converged code is far cheaper to run than a lone lane in a
     // divergent branch); lane 0 arms the barriers and issues the copies.
     uint32_t a_slot = 0, a_ph = 1, r_slot = 0, r_ph = 1;     // "empty" barriers: first pass is free
-    const uint32_t sa = p.sa;
+    uint32_t w_slot = 0, w_ph = 1;                            // dense operand only
+    const uint32_t sa = p.sa, wsn = p.ws;
     const int raw_x_step = raw_row_bytes(BITS);
     for (int b0 = 0; b0 < my_tiles; b0 += nbb) {
       const int nb = min(nbb, my_tiles - b0);
       for (int g = 0; g < G; ++g) {
-        if ((!stationary || b0 == 0) && (g % RG) == 0) {
+        if (dense) {
+          if (!stationary || b0 == 0) {
+            const uint32_t wi = stationary ? static_cast<uint32_t>(g) : w_slot;
+            if (!stationary) ok = ok && mbar_wait_relaxed(&w_empty[wi], w_ph, 32);
+            if (lane == 0 && ok) {
+              mbar_arrive_expect_tx(&w_full[wi], static_cast<uint32_t>(bn) * 128u);
+              tma_load_2d(sW + wi * bn * 128, &tm_w, &w_full[wi], g * 64, n0);
+            }
+            __syncwarp();
+            if (!stationary) {
+              const bool wrap = w_slot + 1 == wsn;
+              w_slot = wrap ? 0u : w_slot + 1;
+              w_ph ^= wrap ? 1u : 0u;
+            }
+          }
+        } else if ((!stationary || b0 == 0) && (g % RG) == 0) {
           ok = ok && mbar_wait_relaxed(&raw_empty[r_slot], r_ph);
           if (lane == 0 && ok) {
             mbar_arrive_expect_tx(&raw_full[r_slot], static_cast<uint32_t>(bn) * raw_row_bytes(BITS));
@@ -241,6 +260,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
       if (lane == 0) stamp(8 + 2 * batch);
       const bool w_waits = !stationary || b0 == 0;   // a stationary slab is built once
       const bool st = tr != nullptr && batch == 2 && lane == 0;
+      const uint32_t leader = lane == 0 ? 1u : 0u;
       if (!w_waits && nb == 1) {
         // steady state of a stationary slab: nothing but "A stage landed -> four MMAs -> free the stage"
         const uint32_t d = tmem_base + (buf0 & 1) * 256;
@@ -248,15 +268,12 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
           ok = ok && mbar_wait_spin(&a_full[a_slot], a_ph);
           const uint64_t da = desc_hi | (a_base + a_slot * a_step);
           const uint64_t db = desc_hi | (w_base + g * w_step);
-          if (lane == 0) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              umma_f16(d, da + 2 * k, db + 2 * k, idesc, (g > 0 || k > 0) ? 1u : 0u);
-              if (st && g < 8) tr[64 + g * 8 + k] = clock64();
-            }
-            umma_commit(&a_empty[a_slot]);
+          for (int k = 0; k < 4; ++k) {
+            umma_f16_if(leader, d, da + 2 * k, db + 2 * k, idesc, (g > 0 || k > 0) ? 1u : 0u);
+            if (st && g < 8) tr[64 + g * 8 + k] = clock64();
           }
-          __syncwarp();
+          umma_commit_if(leader, &a_empty[a_slot]);
           const bool wrap = a_slot + 1 == sa;
           a_slot = wrap ? 0u : a_slot + 1;
           a_ph ^= wrap ? 1u : 0u;
@@ -428,7 +445,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
     const int chunk = ptid & 7;
     const int units = (bn * 8 + kWsProducerThreads - 1 - ptid) / kWsProducerThreads;
     // fold the slab's statistics once: (sigma, mu') as one half2 word per (row, group)
-    if (my_tiles > 0) {
+    if (my_tiles > 0 && !dense) {
       for (int i = ptid; i < bn * G; i += kWsProducerThreads) {
         const long long si = static_cast<long long>(n0) * G + i;
         const float sigma = __ldg(p.sg_w + si);
@@ -438,7 +455,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
       asm volatile("bar.sync 1, %0;" ::"n"(kWsProducerThreads) : "memory");   // producer warps only
     }
     for (int f = 0; f < fills && ok; ++f) {
-      if (my_tiles == 0) break;
+      if (my_tiles == 0 || dense) break;
       for (int g = 0; g < G && ok; ++g) {
         const uint32_t rslot = r_slot;
         if ((g % RG) == 0) ok = mbar_wait_relaxed(&raw_full[rslot], r_ph);

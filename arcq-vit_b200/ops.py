@@ -225,16 +225,48 @@ def pack_codes(codes: torch.Tensor, bits: int) -> torch.Tensor:
     return out
 
 
+def dense_weight_gemm(xhat: torch.Tensor, w16: torch.Tensor, bias, out_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """fp16 reconstructed activation [M,K] x fp16 weight [N,K] (+ fp32 bias) -> [M,N]: the ``F.linear`` of the
+    reference's on-the-fly forward (arcq_packed_on_the_fly.py:160) on the weight ``dequant`` wrote."""
+    lib = _cabi.load()
+    xhat = _dev(xhat, "xhat", torch.float16)
+    w16 = _dev(w16, "w16", torch.float16)
+    if out_dtype not in (torch.float32, torch.float16):
+        raise RuntimeError("out_dtype must be float32 or float16")
+    M, K = xhat.shape
+    N = w16.shape[0]
+    if w16.dim() != 2 or w16.shape[1] != K:
+        raise RuntimeError(f"weight {tuple(w16.shape)} does not match K={K}")
+    b = None
+    if bias is not None and bias.numel() > 0:
+        b = _dev(bias, "bias", torch.float32)
+        if b.numel() != N:
+            raise RuntimeError("bias must have out_features entries")
+    y = torch.empty((M, N), dtype=out_dtype, device=xhat.device)
+    if M == 0:
+        return y
+    rc = lib.arcq_dense_weight_gemm(xhat.data_ptr(), w16.data_ptr(), b.data_ptr() if b is not None else None,
+                                    M, N, K, y.data_ptr(), _DT[out_dtype], _stream())
+    _check(rc, "arcq_dense_weight_gemm")
+    return y
+
+
 def dequant(packed, center, scale, code_sum, codebook, bits: int, group_size: int,
-            out_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+            out_dtype: torch.dtype = torch.float16, out: torch.Tensor = None) -> torch.Tensor:
     """Packed codes + statistics -> [R, K] matrix; what the reference's ``unpack_weight_triton``
-    (arcq_packed_triton.py:77-120) writes.  For tests and debugging only."""
+    (arcq_packed_triton.py:77-120) writes.  ``out``: write into this buffer (first R*K elements) instead
+    of allocating, as the reference does with its ``_weight_buffer``."""
     lib = _cabi.load()
     packed = _dev(packed, "packed", torch.uint8)
     center, scale, code_sum, codebook = (_dev(t, "stats", torch.float32) for t in (center, scale, code_sum, codebook))
     R, G = center.shape
     K = G * group_size
-    out = torch.empty((R, K), dtype=out_dtype, device=packed.device)
+    if out is not None:
+        if out.dtype != out_dtype or not out.is_cuda or not out.is_contiguous() or out.numel() < R * K:
+            raise RuntimeError("out must be a contiguous CUDA buffer of out_dtype with at least R*K elements")
+        out = out.view(-1)[: R * K].view(R, K)
+    else:
+        out = torch.empty((R, K), dtype=out_dtype, device=packed.device)
     _check(lib.arcq_dequant(packed.data_ptr(), center.data_ptr(), scale.data_ptr(), code_sum.data_ptr(),
                             codebook.data_ptr(), bits, group_size, R, K, out.data_ptr(), _DT[out_dtype], _stream()),
            "arcq_dequant")

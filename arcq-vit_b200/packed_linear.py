@@ -20,6 +20,8 @@ checkpoints back): ``ARCQPackedLinear.from_state_dict`` / ``from_buffers``.
 """
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Optional, Tuple
 
@@ -257,6 +259,37 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
     # the module can apply the GELU that precedes it in an MLP block while it quantises its input
     supports_pre_gelu = True
 
+    # How the weight reaches the tensor cores.  "packed": rebuilt from the codes inside the GEMM kernel, never
+    # in HBM.  "dense": unpacked into an fp16 scratch matrix every forward (the reference's own data flow,
+    # arcq_packed_on_the_fly.py:147-160, with its `_weight_buffer`) and read by TMA.  "auto" takes the dense
+    # form where it measured faster: K too long for the rebuilt slab to stay in shared memory (fc2) and
+    # enough rows that the extra launch does not matter.
+    weight_form = os.environ.get("ARCQ_WEIGHT_FORM", "auto")
+    _scratch: dict = {}
+
+    def _weight_scratch(self) -> torch.Tensor:
+        """fp16 scratch of at least N*K elements: the caller's `_weight_buffer` if one was attached (as
+        scripts/benchmark_arcq_on_the_fly.py:189-191 does), else one buffer per (device, stream) shared by all
+        layers -- they run one after the other on that stream."""
+        need = self.out_features * self.in_features
+        buf = getattr(self, "_weight_buffer", None)
+        if buf is not None and buf.is_cuda and buf.dtype == torch.float16 and buf.is_contiguous() and buf.numel() >= need:
+            return buf
+        dev = self.packed_weight_codes.device
+        key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+        buf = ARCQPackedLinearOnTheFly._scratch.get(key)
+        if buf is None or buf.numel() < need:
+            buf = torch.empty(need, dtype=torch.float16, device=dev)
+            ARCQPackedLinearOnTheFly._scratch[key] = buf
+        return buf
+
+    def _use_dense(self, rows: int) -> bool:
+        if self.weight_form == "dense":
+            return True
+        if self.weight_form == "packed":
+            return False
+        return self.in_features > 384 and rows >= 2048
+
     def forward(self, x: torch.Tensor, pre_gelu: bool = False) -> torch.Tensor:
         """``pre_gelu=True``: x is the pre-activation of the GELU in front of this layer; the result
         equals ``forward(F.gelu(x))`` with the GELU fused into the activation quantizer."""
@@ -270,9 +303,15 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
             # then weight unpack + contraction + bias (its steps 3-5) in one persistent kernel
             x_hat = ops.quantize_activation_dequant(x2, self.activation_thresholds, self.activation_codebook,
                                                     self.bits, self.group_size, torch.float16, pre_gelu)
-            y = ops.packed_weight_gemm(x_hat, self.packed_weight_codes, self.weight_center, self.weight_scale,
-                                       self.weight_code_sum, self.weight_codebook, bias, self.bits,
-                                       self.group_size, torch.float16)
+            if self._use_dense(x2.shape[0]):
+                w16 = ops.dequant(self.packed_weight_codes, self.weight_center, self.weight_scale,
+                                  self.weight_code_sum, self.weight_codebook, self.bits, self.group_size,
+                                  torch.float16, out=self._weight_scratch())
+                y = ops.dense_weight_gemm(x_hat, w16, bias, torch.float16)
+            else:
+                y = ops.packed_weight_gemm(x_hat, self.packed_weight_codes, self.weight_center, self.weight_scale,
+                                           self.weight_code_sum, self.weight_codebook, bias, self.bits,
+                                           self.group_size, torch.float16)
         else:
             # shapes the persistent kernel does not take (e.g. 3-bit rows of 72 bytes): packed codes both sides
             packed_x, mu, sg, cs = ops.quantize_activation(x2, self.activation_thresholds, self.activation_codebook,

@@ -248,3 +248,50 @@ class GraphedModel:
         self.static_in.copy_(x, non_blocking=True)
         self.graph.replay()
         return self.static_out
+
+
+class HostPipeline:
+    """Feeds pinned host batches to a model (or a ``GraphedModel``) and returns the logits in pinned host
+    memory.  Batch i+1 is copied to the device on a second stream while batch i computes, and the caller reads
+    the logits of batch i-1 meanwhile; every batch still pays its own host-to-device copy and its own
+    device-to-host read.  Two device staging buffers and two host result buffers alternate."""
+
+    def __init__(self, runner, example_host: torch.Tensor, out_shape, device=None, out_dtype=torch.float16):
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.runner = runner
+        self.copy_stream = torch.cuda.Stream(device=device)
+        self.stage = [torch.empty(example_host.shape, dtype=example_host.dtype, device=device) for _ in range(2)]
+        self.out_host = [torch.empty(tuple(out_shape), dtype=out_dtype).pin_memory() for _ in range(2)]
+        self.h2d_done = [torch.cuda.Event() for _ in range(2)]
+        self.slot_free = [torch.cuda.Event() for _ in range(2)]
+        self.out_done = [torch.cuda.Event() for _ in range(2)]
+
+    def run(self, host_batches, on_result=None) -> int:
+        """Process an iterable of pinned host tensors; ``on_result(logits_host)`` is called once per batch,
+        in order, when that batch's logits have arrived.  Returns the number of batches."""
+        cur = torch.cuda.current_stream()
+        prev, n = None, 0
+        for hb in host_batches:
+            s = n & 1
+            with torch.cuda.stream(self.copy_stream):
+                self.copy_stream.wait_event(self.slot_free[s])      # the step that read this buffer is over
+                self.stage[s].copy_(hb, non_blocking=True)
+                self.h2d_done[s].record(self.copy_stream)
+            cur.wait_event(self.h2d_done[s])
+            with torch.no_grad():
+                y = self.runner(self.stage[s])
+            self.slot_free[s].record(cur)
+            self.out_host[s].copy_(y, non_blocking=True)
+            self.out_done[s].record(cur)
+            if prev is not None:
+                self.out_done[prev].synchronize()
+                if on_result is not None:
+                    on_result(self.out_host[prev])
+            prev = s
+            n += 1
+        if prev is not None:
+            self.out_done[prev].synchronize()
+            if on_result is not None:
+                on_result(self.out_host[prev])
+        return n
+

@@ -294,22 +294,19 @@ def run_gpu_arm(a):
     sync_all()
     torch.cuda.profiler.stop()
     ms = e0.elapsed_time(e1)
-    # ---- end to end: pinned host batch in, logits out, every step
-    stage = torch.empty_like(dev_batches[0])
-    host_logits = torch.empty(B, 1000, dtype=torch.float16).pin_memory()
-    for i in range(3):
-        stage.copy_(host_batches[i % n_rot], non_blocking=True)
-        host_logits.copy_(step(stage), non_blocking=True)
+    # ---- end to end through the package's host-facing runner: every step copies its pinned host batch in and
+    # its logits out; the copy of batch i+1 overlaps the forward of batch i, the caller reads logits i-1 meanwhile
+    pipe = pkg.HostPipeline(step, host_batches[0], (B, 1000), dev)
+    seen = []
+    pipe.run((host_batches[i % n_rot] for i in range(3)), on_result=lambda t: seen.append(float(t[0, 0])))
     sync_all()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
-    for i in range(a.steps):
-        stage.copy_(host_batches[i % n_rot], non_blocking=True)
-        host_logits.copy_(step(stage), non_blocking=True)
-        torch.cuda.current_stream().synchronize()       # the caller reads the logits before the next batch
+    pipe.run((host_batches[i % n_rot] for i in range(a.steps)), on_result=lambda t: seen.append(float(t[0, 0])))
     f1.record()
     sync_all()
     ms_e2e = f0.elapsed_time(f1)
+    host_logits = pipe.out_host[0]
     clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)

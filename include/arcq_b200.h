@@ -142,6 +142,18 @@ int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const flo
                             void* y, int y_dtype, void* stream);
 
 /*
+ * The same linear with the weight given as an fp16 matrix: y[m,n] = bias[n] + sum_k xhat[m,k] * w16[n,k].
+ * Replaces the cuBLAS F.linear of the reference's on-the-fly forward on its unpacked weight buffer,
+ * FQ/fair_qat/arcq_packed_on_the_fly.py:160; w16 is what arcq_dequant (the reference's
+ * unpack_weight_triton) writes.  Same persistent kernel as arcq_packed_weight_gemm with the weight
+ * sub-tiles brought in by TMA instead of rebuilt; the faster of the two forms when few row tiles share a
+ * rebuilt slab (large K with small N).  The caller owns w16 (a scratch buffer it may reuse between layers).
+ *   xhat fp16 [M,K], w16 fp16 [N,K], both 16-byte aligned;  K % 64 == 0;  N % 16 == 0;  y [M,N] fp16 or fp32.
+ */
+int arcq_dense_weight_gemm(const void* xhat, const void* w16, const float* bias, int64_t M, int64_t N,
+                           int64_t K, void* y, int y_dtype, void* stream);
+
+/*
  * Residual add + LayerNorm over fp16 rows, the glue between the packed linears of a transformer block:
  *   s = fp16(x + y), written to sum_out (y and sum_out may both be NULL: plain LayerNorm of x);
  *   h = fp16((s - mean) * rsqrt(var + eps) * gamma + beta), statistics in fp32, biased variance.
@@ -171,8 +183,9 @@ int arcq_pack_codes(const uint8_t* codes, int64_t rows, int64_t length, int bits
 /*
  * Reconstruct an fp16/fp32 matrix from packed codes and statistics:
  * out = mu + sigma*(cb[c] - codesum/gs).  Replaces unpack_weight_triton,
- * FQ/fair_qat/arcq_packed_triton.py:77-120 (kernel :11-74); kept for tests and
- * debugging -- the linear above never materialises this matrix.
+ * FQ/fair_qat/arcq_packed_triton.py:77-120 (kernel :11-74).  Feeds arcq_dense_weight_gemm (into a
+ * scratch buffer, every forward, as the reference does); arcq_packed_weight_gemm never materialises
+ * this matrix.
  */
 int arcq_dequant(const uint8_t* packed, const float* mu, const float* sigma, const float* codesum,
                  const float* codebook, int bits, int group_size, int64_t rows, int64_t K,

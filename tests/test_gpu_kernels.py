@@ -514,3 +514,70 @@ def test_quantizer_with_a_threshold_at_zero_and_with_close_thresholds(pkg, oracl
     got = _dequant_with_stats(pkg, pre, tht, cbt, 4, pre_gelu=True)[0]
     assert float((want == got).float().mean()) > 0.999
     assert pkg.ops.device_status() == 0
+
+
+def test_fused_gelu_over_every_fp16_input(pkg, cuda_device):
+    """The fused GELU must store what a separate fp16 GELU kernel stores.  Every finite fp16 value goes through
+    it (shuffled, so small and large arguments share warps) and the reconstruction is compared with the one
+    computed from torch's GELU output."""
+    vals = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.float16)
+    vals = vals[torch.isfinite(vals)]
+    gen = torch.Generator().manual_seed(11)
+    reps = 20                                                     # 63 488 values x 40 = 39 680 groups
+    by_size = torch.argsort(vals.float().abs(), stable=True)      # groups of like magnitude: small values count
+    idx = torch.cat([torch.randperm(vals.numel(), generator=gen) for _ in range(reps)] + [by_size] * reps)
+    pre = vals[idx].reshape(-1, 2560).to(cuda_device)
+    pre = torch.where(pre.abs() > 30000, pre.sign() * 30000, pre)  # keep group statistics finite
+    cb = torch.linspace(-2.6, 2.55, 16, device=cuda_device)
+    th = (cb[:-1] + cb[1:]) / 2
+    act = torch.nn.functional.gelu(pre)
+    want = pkg.ops.quantize_activation_dequant(act, th, cb, 4, 64, torch.float16)
+    got = pkg.ops.quantize_activation_dequant(pre, th, cb, 4, 64, torch.float16, True)
+    groups_equal = float((want.view(-1, 64) == got.view(-1, 64)).all(dim=1).float().mean())
+    _report("fused_gelu_all_fp16_inputs", groups_equal=groups_equal)
+    # a differing GELU value changes its whole group's statistics; 3 such inputs in 63 488 can touch 0.3 % of groups
+    assert groups_equal > 0.99, groups_equal
+    assert pkg.ops.device_status() == 0
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("M,K,N", [(1, 64, 16), (129, 128, 48), (197, 384, 1152), (300, 1536, 384), (1000, 768, 2304),
+                                   (64 * 197, 1536, 384), (64 * 197, 384, 1536)])
+def test_dense_weight_gemm_matches_an_fp64_product(pkg, cuda_device, M, K, N, out_dtype):
+    """The persistent kernel with an fp16 weight matrix as its second operand (sub-tiles by TMA, nothing
+    rebuilt): against the fp64 product of the same fp16 operands."""
+    gen = torch.Generator().manual_seed(M + K + N)
+    x = torch.randn(M, K, generator=gen).half().to(cuda_device)
+    w = (torch.randn(N, K, generator=gen) * 0.05).half().to(cuda_device)
+    b = torch.randn(N, generator=gen).to(cuda_device)
+    y = pkg.ops.dense_weight_gemm(x, w, b, out_dtype)
+    ref = x.double() @ w.double().t() + b.double()
+    err = float((y.double() - ref).abs().max() / ref.pow(2).mean().sqrt())
+    assert y.dtype == out_dtype and err < (2e-3 if out_dtype == torch.float16 else 2e-5), err
+    y0 = pkg.ops.dense_weight_gemm(x, w, None, out_dtype)
+    assert float((y0.double() - (ref - b.double())).abs().max() / ref.pow(2).mean().sqrt()) < 2e-3
+    assert pkg.ops.device_status() == 0
+
+
+def test_dense_route_of_the_linear_equals_the_packed_route(pkg, oracle, golden, cuda_device):
+    """Unpack into scratch + dense GEMM (the reference's data flow) against the in-kernel rebuild: the two weight
+    forms differ only in how W^ is rounded to fp16, so outputs agree far inside the parity tolerance."""
+    rng = np.random.default_rng(21)
+    M, K, N, bits = 2100, 1536, 384, 4
+    X = rng.standard_normal((M, K), dtype=np.float32)
+    W = (rng.standard_normal((N, K), dtype=np.float32) * 0.03).astype(np.float32)
+    cb = np.concatenate([-np.linspace(0, 2.6, 8)[1:][::-1], [0.0], np.linspace(0, 2.58, 9)[1:]]).astype(np.float32)
+    th = ((cb[:-1] + cb[1:]) / np.float32(2)).astype(np.float32)
+    thd, cbd = _t(th, cuda_device), _t(cb, cuda_device)
+    pw, mw, sw, cw = pkg.ops.quantize_activation(_t(W, cuda_device), thd, cbd, bits, 64)
+    xh = pkg.ops.quantize_activation_dequant(_t(X, cuda_device).half(), thd, cbd, bits, 64, torch.float16)
+    y_packed = pkg.ops.packed_weight_gemm(xh, pw, mw, sw, cw, cbd, None, bits, 64, torch.float16)
+    scratch = torch.empty(N * K + 100, dtype=torch.float16, device=cuda_device)
+    w16 = pkg.ops.dequant(pw, mw, sw, cw, cbd, bits, 64, torch.float16, out=scratch)
+    assert w16.data_ptr() == scratch.data_ptr() and tuple(w16.shape) == (N, K)
+    codes, mu, sg, cs = oracle.quantize(W, th, cb, 64)
+    assert float((w16.float().cpu() - torch.from_numpy(oracle.dequant(codes, mu, sg, cb, 64))).abs().max()) < 1e-3
+    y_dense = pkg.ops.dense_weight_gemm(xh, w16, None, torch.float16)
+    rms = float(y_packed.float().pow(2).mean().sqrt())
+    assert float((y_dense.float() - y_packed.float()).abs().max()) < 1e-2 * rms
+    assert pkg.ops.device_status() == 0

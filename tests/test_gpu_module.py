@@ -119,3 +119,23 @@ def test_product_side_calibration_builds_a_working_model(pkg, cuda_device):
     # 4-bit quantisation perturbs but does not destroy the logits
     assert float((y_q - y_fp).abs().max()) < 1.0
     assert pkg.ops.device_status() == 0
+
+
+def test_host_pipeline_returns_each_batch_in_order(pkg, cuda_device):
+    """Pinned host batches through the double-buffered runner: same logits as calling the model on each batch,
+    delivered in order, one result per batch (odd count, so both buffer slots end a run)."""
+    m = pkg.create_vit("deit_tiny", seed=4).half().to(cuda_device)
+    gen = torch.Generator().manual_seed(9)
+    host = [torch.randn(4, 3, 224, 224, generator=gen).half().pin_memory() for _ in range(5)]
+    with torch.no_grad():
+        q = pkg.quantise_model(m, host[0].to(cuda_device), 4)
+        want = [q(h.to(cuda_device)).cpu() for h in host]
+    runner = pkg.GraphedModel(q, host[0].to(cuda_device))
+    pipe = pkg.HostPipeline(runner, host[0], (4, 1000), cuda_device)
+    got = []
+    assert pipe.run(iter(host), on_result=lambda t: got.append(t.clone())) == 5
+    assert len(got) == 5
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+    assert pipe.run(iter([])) == 0
+    assert pkg.ops.device_status() == 0
