@@ -15,7 +15,7 @@ DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 
 # every symbol include/arcq_b200.h declares
 EXPORTS = (
-    "arcq_version", "arcq_last_error_string", "arcq_device_status", "arcq_debug_trace", "arcq_act_quant", "arcq_gelu_act_quant", "arcq_packed_gemm", "arcq_packed_weight_gemm", "arcq_dense_weight_gemm", "arcq_add_layernorm",
+    "arcq_version", "arcq_last_error_string", "arcq_device_status", "arcq_debug_trace", "arcq_act_quant", "arcq_gelu_act_quant", "arcq_packed_gemm", "arcq_packed_weight_gemm", "arcq_dense_weight_gemm", "arcq_packed_linear_static_scratch", "arcq_add_layernorm",
     "arcq_unpack_codes", "arcq_pack_codes", "arcq_dequant",
 )
 
@@ -46,6 +46,7 @@ def load() -> ctypes.CDLL:
     lib.arcq_packed_gemm.argtypes = [vp] * 11 + [ci, ci, i64, i64, i64, vp, ci, vp]
     lib.arcq_packed_weight_gemm.argtypes = [vp] * 7 + [ci, ci, i64, i64, i64, vp, ci, vp]
     lib.arcq_dense_weight_gemm.argtypes = [vp, vp, vp, i64, i64, i64, vp, ci, vp]
+    lib.arcq_packed_linear_static_scratch.argtypes = lib.arcq_packed_weight_gemm.argtypes
     lib.arcq_add_layernorm.argtypes = [vp, vp, vp, vp, ctypes.c_float, i64, i64, vp, vp, vp]
     lib.arcq_unpack_codes.argtypes = [vp, i64, i64, ci, vp, vp]
     lib.arcq_pack_codes.argtypes = [vp, i64, i64, ci, vp, vp]

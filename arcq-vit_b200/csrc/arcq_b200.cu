@@ -1,6 +1,7 @@
 // C ABI of the B200 back end: argument checks, launch configuration, error reporting.
 // The kernels live in the .cuh files included below; this is the only translation unit.
 #include <cuda_runtime.h>
+#include <mutex>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
@@ -565,6 +566,69 @@ int arcq_dequant(const uint8_t* packed, const float* mu, const float* sigma, con
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "dequant launch");
   return ARCQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Linear with the library's own weight scratch.
+//
+// The dense route above needs room for the unpacked fp16 weight, and so far the caller brings it.  Some
+// callers have no way to: a C host that binds this ABI from a runtime whose device memory was handed out in
+// full at start-up, or a serving loop in which a device allocation (and the device-wide wait it may imply) is
+// not acceptable once requests are flowing.  For them the scratch lives in the library image itself: a
+// file-scope device array, sized for the largest DeiT-B linear (768 x 3072 fp16 values, 4.5 MB per device).
+// Nothing here allocates or frees memory.
+//  * Set-up: the array's device address is looked up once per device, on the first call made with that
+//    device current.  That look-up is host-side work of the CUDA runtime; make the first call outside any
+//    stream capture, later calls only launch kernels.
+//  * Nothing has to start at zero: every element the contraction reads was written by the unpack kernel of
+//    the same call, which is ordered before it on `stream`.
+//  * One array per device: two calls in flight at once on the same device (different streams or host
+//    threads) would overwrite each other's weight.  Calls must be ordered one after the other.
+constexpr long long kStaticWeightElems = ARCQ_STATIC_WEIGHT_ELEMS;
+static __device__ __align__(256) __half g_static_w16[kStaticWeightElems];
+
+static __half* static_weight_scratch() {
+  constexpr int kMaxDevices = 64;
+  static __half* cached[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    fail(ARCQ_E_CUDA, "no current CUDA device (or device index above %d)", kMaxDevices - 1);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_w16);
+    if (e != cudaSuccess || p == nullptr) {
+      cuda_fail(e, "address of the static weight scratch");
+      return nullptr;
+    }
+    cached[dev] = static_cast<__half*>(p);
+  }
+  return cached[dev];
+}
+
+int arcq_packed_linear_static_scratch(const void* xhat, const uint8_t* packed_w, const float* mu_w,
+                                      const float* sigma_w, const float* codesum_w, const float* w_codebook,
+                                      const float* bias, int bits, int group_size, int64_t M, int64_t N, int64_t K,
+                                      void* y, int y_dtype, void* stream) {
+  if (!xhat || !packed_w || !mu_w || !sigma_w || !codesum_w || !w_codebook || !y)
+    return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (M < 0 || N <= 0 || K <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape M=%lld N=%lld K=%lld", (long long)M,
+                                              (long long)N, (long long)K);
+  if (group_size != 64) return fail(ARCQ_E_UNSUPPORTED, "group_size %d: only 64 is built", group_size);
+  if (N > kStaticWeightElems || K > kStaticWeightElems || N * K > kStaticWeightElems)
+    return fail(ARCQ_E_TOO_LARGE, "weight of %lld x %lld values exceeds the static scratch of %lld values; "
+                                  "use arcq_dequant + arcq_dense_weight_gemm with a buffer of your own",
+                (long long)N, (long long)K, (long long)kStaticWeightElems);
+  __half* const w16 = static_weight_scratch();
+  if (w16 == nullptr) return ARCQ_E_CUDA;
+  if (M == 0) return ARCQ_OK;
+  const int rc = arcq_dequant(packed_w, mu_w, sigma_w, codesum_w, w_codebook, bits, group_size, N, K, w16,
+                              ARCQ_DT_F16, stream);
+  if (rc != ARCQ_OK) return rc;
+  return arcq_dense_weight_gemm(xhat, w16, bias, M, N, K, y, y_dtype, stream);
 }
 
 }  // extern "C"

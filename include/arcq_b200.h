@@ -154,6 +154,22 @@ int arcq_dense_weight_gemm(const void* xhat, const void* w16, const float* bias,
                            int64_t K, void* y, int y_dtype, void* stream);
 
 /*
+ * The packed linear (same arguments and result as arcq_packed_weight_gemm) for callers that cannot provide
+ * device memory: the weight is unpacked into a scratch array that is part of the library image (one per
+ * device, ARCQ_STATIC_WEIGHT_ELEMS fp16 values) and contracted from there, i.e. arcq_dequant followed by
+ * arcq_dense_weight_gemm without a caller buffer.  No reference counterpart: the reference allocates its
+ * `_weight_buffer` with torch.  Allocates and frees nothing.  N*K above the capacity returns
+ * ARCQ_E_TOO_LARGE.  The first call on a device resolves the array's address (host-side set-up: make it
+ * outside stream capture).  Calls on one device must not overlap in time -- they share the array.
+ * Limits as arcq_dense_weight_gemm: K % 64 == 0, N % 16 == 0, group_size 64, 16-byte aligned xhat / y.
+ */
+#define ARCQ_STATIC_WEIGHT_ELEMS (768LL * 3072LL)
+int arcq_packed_linear_static_scratch(const void* xhat, const uint8_t* packed_w, const float* mu_w,
+                                      const float* sigma_w, const float* codesum_w, const float* w_codebook,
+                                      const float* bias, int bits, int group_size, int64_t M, int64_t N,
+                                      int64_t K, void* y, int y_dtype, void* stream);
+
+/*
  * Residual add + LayerNorm over fp16 rows, the glue between the packed linears of a transformer block:
  *   s = fp16(x + y), written to sum_out (y and sum_out may both be NULL: plain LayerNorm of x);
  *   h = fp16((s - mean) * rsqrt(var + eps) * gamma + beta), statistics in fp32, biased variance.
