@@ -46,6 +46,34 @@ template <typename T, int PRE> __device__ __forceinline__ float pre_op(float x) 
   return x;
 }
 
+// Exact GELU, 0.5*x*(1+erf(x/sqrt 2)) in fp32, for code that all 32 lanes of a warp run together.
+// erf(z) for |z| < 0.9277 is z*P(z*z) with a degree-7 least-squares fit on Chebyshev nodes (max error 1e-11
+// before rounding); over every fp16 input in that range the GELU rounded to fp16 differs from the exactly
+// rounded one for 3 inputs of 31 360 -- the library erff gives 2.  Larger arguments call erff, but only when
+// some lane of the warp needs it: the branch is warp-uniform, so the common case (pre-activations of a few
+// units at most) never executes the long path.  Each element's result depends on its own value only.
+__device__ __forceinline__ float gelu_warp(float x) {
+  const float z = x * 0.70710678118654752440f;
+  const float s = z * z;
+  float r = -1.0267135621688794e-05f;
+  r = fmaf(r, s, 0.00011447568977018818f);
+  r = fmaf(r, s, -0.0008505592122673988f);
+  r = fmaf(r, s, 0.005222289357334375f);
+  r = fmaf(r, s, -0.026865806430578232f);
+  r = fmaf(r, s, 0.11283788084983826f);
+  r = fmaf(r, s, -0.37612637877464294f);
+  r = fmaf(r, s, 1.128379225730896f);
+  float e = z * r;
+  const bool big = !(fabsf(z) < 0.9277f);
+  if (__any_sync(0xffffffffu, big)) {
+    const float el = erff(z);
+    e = big ? el : e;
+  }
+  return x * 0.5f * (1.0f + e);
+}
+// The same, rounded to the element type T: the value a separate GELU kernel would have stored.
+template <typename T> __device__ __forceinline__ float gelu_rounded_warp(float x) { return round_to<T>(gelu_warp(x)); }
+
 // Sum of the value held by the 8 lanes of an octet, lane 0 first, as a chain of fp32 additions.
 __device__ __forceinline__ float octet_chain_sum(float p, int octet_base) {
   float s = __shfl_sync(0xffffffffu, p, octet_base);

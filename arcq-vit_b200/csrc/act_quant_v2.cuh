@@ -70,7 +70,7 @@ template <> struct Aq2Row<__half> { static constexpr int kBytes = 128, kPitch = 
 template <> struct Aq2Row<__nv_bfloat16> { static constexpr int kBytes = 128, kPitch = 144; };
 
 template <typename T> __host__ __device__ constexpr size_t aq2_smem_bytes() {
-  return 2 * kAq2Threads * Aq2Row<T>::kPitch + 16 * kAq2Threads * 4 + 3 * 16 * 4 + kAq2Cells * 4 + 16;
+  return 2 * kAq2Threads * Aq2Row<T>::kPitch + 16 * kAq2Threads * 4 + 4 * 16 * 4 + kAq2Cells * 4 + 16;
 }
 
 // unpack one staged row into 64 floats
@@ -110,32 +110,6 @@ template <> __device__ __forceinline__ void aq2_load_row<__nv_bfloat16>(const ui
   }
 }
 
-// Exact GELU, 0.5*x*(1+erf(x/sqrt 2)) in fp32 rounded to T, for a loop that all 32 lanes of a warp run
-// together.  erf(z) for |z| < 0.9277 is z*P(z*z) with a degree-7 least-squares fit on Chebyshev nodes (max
-// error 1e-11 before rounding); over every fp16 input in that range the rounded GELU differs from the exactly
-// rounded one for 3 inputs of 31 360 -- the library erff gives 2.  Larger arguments call erff, but only when
-// some lane of the warp needs it: the branch is warp-uniform, so the common case (pre-activations of a few
-// units at most) never executes the long path.  Each element's result depends on its own value only.
-template <typename T> __device__ __forceinline__ float gelu_rounded_warp(float x) {
-  const float z = x * 0.70710678118654752440f;
-  const float s = z * z;
-  float r = -1.0267135621688794e-05f;
-  r = fmaf(r, s, 0.00011447568977018818f);
-  r = fmaf(r, s, -0.0008505592122673988f);
-  r = fmaf(r, s, 0.005222289357334375f);
-  r = fmaf(r, s, -0.026865806430578232f);
-  r = fmaf(r, s, 0.11283788084983826f);
-  r = fmaf(r, s, -0.37612637877464294f);
-  r = fmaf(r, s, 1.128379225730896f);
-  float e = z * r;
-  const bool big = !(fabsf(z) < 0.9277f);
-  if (__any_sync(0xffffffffu, big)) {
-    const float el = erff(z);
-    e = big ? el : e;
-  }
-  return round_to<T>(x * 0.5f * (1.0f + e));
-}
-
 // XH: type of the optional reconstruction output (same byte size as T is not required).
 template <typename T, int BITS, typename XH, bool WRITE_XHAT, int PRE = 0>
 __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* __restrict__ x, long long total_groups,
@@ -158,8 +132,9 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
   float* const s_cb = s_h + 16;                                                             // [16]
   const int tid = threadIdx.x;
 
-  // thresholds, half-gaps to the next float above, codebook; decide whether the division-free test is exact
-  bool exact_r = true;
+  // Per-block set-up, kept short because a block may process a single tile: thresholds, half-gaps to the
+  // next float above and codebook by 16 threads; whether the division-free test is exact by one vote.
+  int my_exact = 1;
   if (tid < 16) {
     float th = __int_as_float(0x7f800000), h = 0.0f;
     if (tid < L - 1) {
@@ -171,44 +146,45 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
         const float up = __int_as_float(th > 0.0f ? b + 1 : b - 1);   // next float toward +inf
         h = __fmul_rn(__fsub_rn(up, th), 0.5f);
       }
+      my_exact = (th == 0.0f || fabsf(th) > 1.0e-15f) ? 1 : 0;
     }
     s_th[tid] = th;
     s_h[tid] = h;
     s_cb[tid] = tid < L ? codebook[tid] : 0.0f;
   }
-#pragma unroll
-  for (int i = 0; i < L - 1; ++i) {
-    const float th = __ldg(thresholds + i);
-    exact_r = exact_r && (th == 0.0f || fabsf(th) > 1.0e-15f);
-  }
-  __syncthreads();
+  const bool exact_r = __syncthreads_and(my_exact) != 0;
 
   // First guess by a uniform grid.  u = (t - th_first) * (C-2) / (th_last - th_first) + 1 puts the thresholds
   // at positions 1..C-1; cell k = floor(u) clamped to 0..C-1 (C = kAq2Cells).  s_guess[k] = number of
-  // thresholds that lie safely below cell k.  If every (slightly widened) cell holds at most one threshold,
-  // the code of a value in cell k is s_guess[k] + (value > that threshold): one table look-up and one exact
-  // comparison instead of a four-step search.  The exact comparison is the same one the search would end
-  // with, so the result is identical; codebooks with two thresholds closer than a cell (1/254 of the
-  // threshold range) fall back to the search.
-  int* const s_guess = reinterpret_cast<int*>(s_cb + 16);      // [kAq2Cells] byte offsets into a table column
+  // thresholds that lie safely below cell k (position < k - 0.05).  If consecutive thresholds are more than
+  // 1.1 cells apart, a cell widened by 0.05 on both sides holds at most one of them, and the code of a value in
+  // cell k is s_guess[k] + (value > that threshold): one table look-up and one exact comparison instead of a
+  // four-step search.  The exact comparison is the same one the search would end with, so the result is
+  // identical; codebooks with closer thresholds (1/231 of the threshold range) fall back to the search.
+  float* const s_pos = s_cb + 16;                               // [16] grid positions of the thresholds, +inf padded
+  int* const s_guess = reinterpret_cast<int*>(s_pos + 16);     // [kAq2Cells] byte offsets into a table column
   float grid_scale = 0.0f, grid_off = 0.0f;
   bool use_guess = false;
   if (L >= 4) {
     const float th_first = s_th[0], th_last = s_th[L - 2];
     grid_scale = static_cast<float>(kAq2Cells - 2) / (th_last - th_first);
     grid_off = 1.0f - th_first * grid_scale;
-    int cell_ok = 1;
-    for (int k = tid; k < kAq2Cells; k += kAq2Threads) {
-      int below = 0, inside = 0;
-      for (int i = 0; i < L - 1; ++i) {
-        const float pos = fmaf(s_th[i], grid_scale, grid_off);
-        below += (pos < static_cast<float>(k) - 0.05f) ? 1 : 0;
-        inside += (pos >= static_cast<float>(k) - 0.05f && pos <= static_cast<float>(k) + 1.05f) ? 1 : 0;
-      }
-      s_guess[k] = below * (kAq2Threads * 4);
-      cell_ok = (inside <= 1) ? cell_ok : 0;
+    int gap_ok = 1;
+    if (tid < 16) {
+      const float pos = tid < L - 1 ? fmaf(s_th[tid], grid_scale, grid_off) : __int_as_float(0x7f800000);
+      s_pos[tid] = pos;
+      if (tid < L - 2) gap_ok = (fmaf(s_th[tid + 1], grid_scale, grid_off) - pos > 1.1f) ? 1 : 0;
     }
-    use_guess = __syncthreads_and(cell_ok) != 0 && exact_r && isfinite(grid_scale);
+    use_guess = __syncthreads_and(gap_ok) != 0 && exact_r && isfinite(grid_scale);
+    for (int k = tid; k < kAq2Cells; k += kAq2Threads) {
+      const float lim = static_cast<float>(k) - 0.05f;          // count of positions below lim: the 15 (or
+      int c = (s_pos[7] < lim) ? 8 : 0;                         // fewer) sorted values are padded to 16 with +inf
+      c += (s_pos[c + 3] < lim) ? 4 : 0;
+      c += (s_pos[c + 1] < lim) ? 2 : 0;
+      c += (s_pos[c] < lim) ? 1 : 0;
+      s_guess[k] = c * (kAq2Threads * 4);
+    }
+    // s_guess is first read after the block-wide barrier that follows the first tile's arrival below
   }
 
   const long long tiles = (total_groups + kAq2Threads - 1) / kAq2Threads;

