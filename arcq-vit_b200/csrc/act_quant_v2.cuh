@@ -70,7 +70,7 @@ template <> struct Aq2Row<__half> { static constexpr int kBytes = 128, kPitch = 
 template <> struct Aq2Row<__nv_bfloat16> { static constexpr int kBytes = 128, kPitch = 144; };
 
 template <typename T> __host__ __device__ constexpr size_t aq2_smem_bytes() {
-  return 2 * kAq2Threads * Aq2Row<T>::kPitch + 16 * kAq2Threads * 4 + 4 * 16 * 4 + kAq2Cells * 4 + 16;
+  return 2 * kAq2Threads * Aq2Row<T>::kPitch + 2 * 16 * kAq2Threads * 4 + 4 * 16 * 4 + kAq2Cells * 4 + 16;
 }
 
 // unpack one staged row into 64 floats
@@ -111,7 +111,8 @@ template <> __device__ __forceinline__ void aq2_load_row<__nv_bfloat16>(const ui
 }
 
 // XH: type of the optional reconstruction output (same byte size as T is not required).
-template <typename T, int BITS, typename XH, bool WRITE_XHAT, int PRE = 0>
+// WRITE_PACKED = false (reconstruction only, `packed` is null): the codes are never assembled into words.
+template <typename T, int BITS, typename XH, bool WRITE_XHAT, int PRE = 0, bool WRITE_PACKED = true>
 __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* __restrict__ x, long long total_groups,
                                                                    const float* __restrict__ thresholds,
                                                                    const float* __restrict__ codebook,
@@ -127,7 +128,8 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
   extern __shared__ __align__(16) uint8_t aq2_smem[];
   uint8_t* const s_stage = aq2_smem;                                                        // 2 x 128 rows
   float* const s_table = reinterpret_cast<float*>(aq2_smem + 2 * kAq2Threads * kPitch);     // [16][128]
-  float* const s_th = s_table + 16 * kTableStride;                                          // [16]
+  float* const s_cbt = s_table + 16 * kTableStride;                                         // [16][128] codebook, same indexing
+  float* const s_th = s_cbt + 16 * kTableStride;                                            // [16]
   float* const s_h = s_th + 16;                                                             // [16]
   float* const s_cb = s_h + 16;                                                             // [16]
   const int tid = threadIdx.x;
@@ -153,6 +155,10 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
     s_cb[tid] = tid < L ? codebook[tid] : 0.0f;
   }
   const bool exact_r = __syncthreads_and(my_exact) != 0;
+  // the codebook laid out like the limit table (entry i of thread t at i*128 + t): the byte offset that selects
+  // a limit selects the codebook value too, and a column is as conflict-free as the limits'
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s_cbt[i * kTableStride + tid] = s_cb[i];
 
   // First guess by a uniform grid.  u = (t - th_first) * (C-2) / (th_last - th_first) + 1 puts the thresholds
   // at positions 1..C-1; cell k = floor(u) clamped to 0..C-1 (C = kAq2Cells).  s_guess[k] = number of
@@ -260,6 +266,7 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
     // accumulates the code (code * kTableStride * 4), so a step is: load, compare, conditional add.
     uint32_t words[8];
     const char* const col = reinterpret_cast<const char*>(my_table);
+    const char* const cbcol = reinterpret_cast<const char*>(s_cbt + tid);
     constexpr int kStep = kTableStride * 4;
     auto classify = [&](auto key_of) {
 #pragma unroll
@@ -273,9 +280,9 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
           if (BITS >= 3) off += (key > *reinterpret_cast<const float*>(col + off + 3 * kStep)) ? 4 * kStep : 0;
           off += (key > *reinterpret_cast<const float*>(col + off + 1 * kStep)) ? 2 * kStep : 0;
           off += (key > *reinterpret_cast<const float*>(col + off)) ? kStep : 0;
-          // kStep = 512 bytes: code = off >> 9; the codebook entry sits at byte offset code * 4 = off >> 7
-          w = (w << 4) | static_cast<uint32_t>(off >> 9);
-          v[8 * c + j] = *reinterpret_cast<const float*>(reinterpret_cast<const char*>(s_cb) + (off >> 7));
+          // kStep = 512 bytes: code = off >> 9; the same offset addresses this thread's codebook column
+          if (WRITE_PACKED) w = (w << 4) | static_cast<uint32_t>(off >> 9);
+          v[8 * c + j] = *reinterpret_cast<const float*>(cbcol + off);
         }
         words[c] = w;
       }
@@ -292,8 +299,8 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
                                     static_cast<unsigned>(kAq2Cells - 1));             // negative -> 0
           int off = s_guess[cell];
           off += (r > *reinterpret_cast<const float*>(col + off)) ? kStep : 0;
-          w = (w << 4) | static_cast<uint32_t>(off >> 9);
-          v[8 * c + j] = *reinterpret_cast<const float*>(reinterpret_cast<const char*>(s_cb) + (off >> 7));
+          if (WRITE_PACKED) w = (w << 4) | static_cast<uint32_t>(off >> 9);
+          v[8 * c + j] = *reinterpret_cast<const float*>(cbcol + off);
         }
         words[c] = w;
       }
@@ -305,7 +312,7 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
     const float code_sum = sum64_ref_order(v);
 
     if (valid) {
-      if (packed != nullptr) {
+      if (WRITE_PACKED && packed != nullptr) {
         if (BITS == 4) {
           uint4* o = reinterpret_cast<uint4*>(packed + gi * 32);
           o[0] = make_uint4(words[0], words[1], words[2], words[3]);

@@ -118,6 +118,11 @@ cudaError_t launch_act_quant_v2(const void* x, long long groups, const float* th
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     k<<<grid, arcq::kAq2Threads, smem, st>>>(xt, groups, th, cb, packed, mu, sg, cs, nullptr);
+  } else if (packed == nullptr) {
+    auto k = arcq::act_quant_v2_kernel<T, BITS, T, true, PRE, false>;
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    k<<<grid, arcq::kAq2Threads, smem, st>>>(xt, groups, th, cb, nullptr, mu, sg, cs, static_cast<T*>(xhat));
   } else {
     auto k = arcq::act_quant_v2_kernel<T, BITS, T, true, PRE>;
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
