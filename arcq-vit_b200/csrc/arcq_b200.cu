@@ -13,6 +13,7 @@
 #include "ptx.cuh"
 #include "act_quant.cuh"
 #include "act_quant_v2.cuh"
+#include "act_quant_v4.cuh"
 #include "codes.cuh"
 #include "packed_gemm.cuh"
 #include "gemm_ws.cuh"
@@ -67,7 +68,7 @@ int sm_count() {
 
 // Tuning overrides for experiments (unset in normal use): ARCQ_WS_BN, ARCQ_WS_SA, ARCQ_WS_WS,
 // ARCQ_WS_STATIONARY, ARCQ_WS_NBB, ARCQ_WS_GRID,
-// ARCQ_WS_TMA_STORE, ARCQ_WS_ROTATE, ARCQ_ACT_QUANT_V1, ARCQ_LN_PLAIN.
+// ARCQ_WS_TMA_STORE, ARCQ_WS_ROTATE, ARCQ_ACT_QUANT_V1, ARCQ_ACT_QUANT_V2, ARCQ_LN_PLAIN.
 int env_int(const char* name, int dflt) {
   const char* v = getenv(name);
   return (v != nullptr && *v != 0) ? atoi(v) : dflt;
@@ -132,6 +133,42 @@ cudaError_t launch_act_quant_v2(const void* x, long long groups, const float* th
   return cudaGetLastError();
 }
 
+// Two-lanes-per-group form of the staged quantizer (16-bit element types): same results, twice the warps.
+template <typename T, int BITS, int PRE = 0>
+cudaError_t launch_act_quant_v4(const void* x, long long groups, const float* th, const float* cb, uint8_t* packed,
+                                float* mu, float* sg, float* cs, void* xhat, cudaStream_t st) {
+  const size_t smem = arcq::aq4_smem_bytes<T>();
+  const long long tiles = (groups + arcq::kAq4Groups - 1) / arcq::kAq4Groups;
+  const long long cap = static_cast<long long>(sm_count()) * 3;
+  const int grid = static_cast<int>(tiles < cap ? tiles : cap);
+  const T* xt = static_cast<const T*>(x);
+  T* xo = static_cast<T*>(xhat);
+  cudaError_t e;
+#define ARCQ_AQ4(WX, WP)                                                                                          \
+  do {                                                                                                           \
+    auto k = arcq::act_quant_v4_kernel<T, BITS, WX, PRE, WP>;                                                    \
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));            \
+    if (e != cudaSuccess) return e;                                                                              \
+    k<<<grid, arcq::kAq4Threads, smem, st>>>(xt, groups, th, cb, packed, mu, sg, cs, xo);                        \
+  } while (0)
+  if (xhat == nullptr) ARCQ_AQ4(false, true);
+  else if (packed == nullptr) ARCQ_AQ4(true, false);
+  else ARCQ_AQ4(true, true);
+#undef ARCQ_AQ4
+  return cudaGetLastError();
+}
+
+template <typename T> struct IsSixteenBit { static constexpr bool value = sizeof(T) == 2; };
+
+template <typename T, int BITS, int PRE>
+cudaError_t launch_staged(bool two_lane, const void* x, long long groups, const float* th, const float* cb,
+                          uint8_t* packed, float* mu, float* sg, float* cs, void* xhat, cudaStream_t st) {
+  if constexpr (IsSixteenBit<T>::value) {
+    if (two_lane) return launch_act_quant_v4<T, BITS, PRE>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
+  }
+  return launch_act_quant_v2<T, BITS, PRE>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
+}
+
 template <typename T, int PRE>
 cudaError_t dispatch_act_quant_bits(int bits, const void* x, int x_dtype, long long groups, const float* th,
                                     const float* cb, uint8_t* packed, float* mu, float* sg, float* cs, void* xhat,
@@ -143,10 +180,15 @@ cudaError_t dispatch_act_quant_bits(int bits, const void* x, int x_dtype, long l
                   (packed == nullptr || aligned(packed, 16)) &&
                   (xhat == nullptr || (xhat_dtype == x_dtype && aligned(xhat, 16)));
   if (v2) {
+    // The two-lanes-per-group form (16-bit inputs) measured faster only where the per-element arithmetic is
+    // long, i.e. with the fused GELU (42 vs 48 us on [12608,1536]); the plain quantizer stays one thread per
+    // group (9.3 vs 10.8 us on [12608,384]).  ARCQ_ACT_QUANT_V2 = 1 / 2 forces the one-lane / two-lane form.
+    const int force = env_int("ARCQ_ACT_QUANT_V2", 0);
+    const bool two_lane = force == 2 || (force == 0 && PRE == 1);
     switch (bits) {
-      case 4: return launch_act_quant_v2<T, 4, PRE>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
-      case 3: return launch_act_quant_v2<T, 3, PRE>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
-      default: return launch_act_quant_v2<T, 2, PRE>(x, groups, th, cb, packed, mu, sg, cs, xhat, st);
+      case 4: return launch_staged<T, 4, PRE>(two_lane, x, groups, th, cb, packed, mu, sg, cs, xhat, st);
+      case 3: return launch_staged<T, 3, PRE>(two_lane, x, groups, th, cb, packed, mu, sg, cs, xhat, st);
+      default: return launch_staged<T, 2, PRE>(two_lane, x, groups, th, cb, packed, mu, sg, cs, xhat, st);
     }
   }
   switch (bits) {

@@ -414,6 +414,15 @@ def test_staged_quantizer_kernel_matches_oracle_and_the_parallel_kernel(pkg, ora
     finally:
         del os.environ["ARCQ_ACT_QUANT_V1"]
     assert torch.equal(p, p1) and torch.equal(m, m1) and torch.equal(s, s1) and torch.equal(c, c1)
+    if dtype != torch.float32:                              # and through the two-lanes-per-group form
+        os.environ["ARCQ_ACT_QUANT_V2"] = "2"
+        try:
+            p2, m2, s2, c2 = pkg.ops.quantize_activation(xd, _t(th, cuda_device), _t(cb, cuda_device), bits, 64)
+            xh2 = pkg.ops.quantize_activation_dequant(xd, _t(th, cuda_device), _t(cb, cuda_device), bits, 64, dtype)
+        finally:
+            del os.environ["ARCQ_ACT_QUANT_V2"]
+        assert torch.equal(p, p2) and torch.equal(m, m2) and torch.equal(s, s2) and torch.equal(c, c2)
+        assert torch.equal(xh2, pkg.ops.quantize_activation_dequant(xd, _t(th, cuda_device), _t(cb, cuda_device), bits, 64, dtype))
     # reconstruction output: one fused multiply-add per value here, three rounded steps in the reference;
     # equal after rounding to a 16-bit type except for rare last-bit cases
     xh = pkg.ops.quantize_activation_dequant(xd, _t(th, cuda_device), _t(cb, cuda_device), bits, 64, dtype)
@@ -580,4 +589,36 @@ def test_dense_route_of_the_linear_equals_the_packed_route(pkg, oracle, golden, 
     y_dense = pkg.ops.dense_weight_gemm(xh, w16, None, torch.float16)
     rms = float(y_packed.float().pow(2).mean().sqrt())
     assert float((y_dense.float() - y_packed.float()).abs().max()) < 1e-2 * rms
+    assert pkg.ops.device_status() == 0
+
+
+def test_two_lane_quantizer_search_and_zero_threshold_paths(pkg, oracle, cuda_device):
+    """The two-lanes-per-group form on codebooks that leave the first-guess path (close thresholds -> search) or
+    have a threshold at zero, fp16 and bf16 inputs, ragged group count, all three outputs."""
+    import os
+    rng = np.random.default_rng(23)
+    X = (rng.standard_normal((1023, 2560), dtype=np.float32) * 0.8).astype(np.float32)      # 40 920 groups
+    X[7, :64] = 0.0
+    os.environ["ARCQ_ACT_QUANT_V2"] = "2"
+    try:
+        for dtype in (torch.float16, torch.bfloat16):
+            x = torch.from_numpy(X).to(dtype)
+            xr = x.float().numpy()
+            for cb in (np.array([-2.5, -2.0, -1.5, -1.0, -0.6, -0.3, -0.1, 0.0, 0.004, 0.008, 0.3, 0.7, 1.1, 1.6, 2.1, 2.6], np.float32),
+                       np.array([-2.4, -1.9, -1.4, -1.0, -0.7, -0.45, -0.25, -0.1, 0.1, 0.25, 0.45, 0.7, 1.0, 1.4, 1.9, 2.4], np.float32)):
+                th = ((cb[:-1] + cb[1:]) / np.float32(2)).astype(np.float32)
+                codes, mu, sg, cs = oracle.quantize(xr, th, cb, 64)
+                p, m, s, c = pkg.ops.quantize_activation(x.to(cuda_device), _t(th, cuda_device), _t(cb, cuda_device), 4, 64)
+                assert np.array_equal(p.cpu().numpy(), oracle.pack(codes, 4))
+                assert np.array_equal(m.cpu().numpy(), mu) and np.array_equal(s.cpu().numpy(), sg)
+                assert np.array_equal(c.cpu().numpy(), cs)
+            # 3-bit and 2-bit packing of the swapped half-words
+            for bits in (3, 2):
+                cb = np.sort(rng.uniform(-2.8, 2.8, 2 ** bits)).astype(np.float32)
+                th = ((cb[:-1] + cb[1:]) / np.float32(2)).astype(np.float32)
+                codes, mu, sg, cs = oracle.quantize(xr, th, cb, 64)
+                p = pkg.ops.quantize_activation(x.to(cuda_device), _t(th, cuda_device), _t(cb, cuda_device), bits, 64)[0]
+                assert np.array_equal(p.cpu().numpy(), oracle.pack(codes, bits))
+    finally:
+        del os.environ["ARCQ_ACT_QUANT_V2"]
     assert pkg.ops.device_status() == 0
