@@ -55,7 +55,7 @@ __device__ __forceinline__ float aq4_group_chain(const float (&p)[4], int lane) 
 }
 
 template <typename T, int BITS, bool WRITE_XHAT, int PRE = 0, bool WRITE_PACKED = true>
-__global__ void __launch_bounds__(kAq4Threads, 3) act_quant_v4_kernel(const T* __restrict__ x, long long total_groups,
+__global__ void __launch_bounds__(kAq4Threads, 4) act_quant_v4_kernel(const T* __restrict__ x, long long total_groups,
                                                                    const float* __restrict__ thresholds,
                                                                    const float* __restrict__ codebook,
                                                                    uint8_t* __restrict__ packed,

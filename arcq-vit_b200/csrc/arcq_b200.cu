@@ -139,7 +139,7 @@ cudaError_t launch_act_quant_v4(const void* x, long long groups, const float* th
                                 float* mu, float* sg, float* cs, void* xhat, cudaStream_t st) {
   const size_t smem = arcq::aq4_smem_bytes<T>();
   const long long tiles = (groups + arcq::kAq4Groups - 1) / arcq::kAq4Groups;
-  const long long cap = static_cast<long long>(sm_count()) * 3;
+  const long long cap = static_cast<long long>(sm_count()) * 4;
   const int grid = static_cast<int>(tiles < cap ? tiles : cap);
   const T* xt = static_cast<const T*>(x);
   T* xo = static_cast<T*>(xhat);
