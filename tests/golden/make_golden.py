@@ -119,7 +119,7 @@ def make_case(name: str, spec: dict, ref) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (ARCQ-ViT)")
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     ref = _import_reference(Path(args.reference))
