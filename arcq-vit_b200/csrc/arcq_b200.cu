@@ -287,7 +287,7 @@ bool choose_ws_config(long long M, long long N, long long K, int bits, bool dens
     const int stream_slots = dense ? 4 : 3;
     int ws = stationary ? G : (G < stream_slots ? G : stream_slots);
     if (!stationary && force_ws > 0 && force_ws <= 16) ws = force_ws;
-    if (ws > 16) continue;
+    if (ws > (stationary ? 32 : 16)) continue;   // barrier slots: 16 full/empty pairs for a ring, 32 full for a stationary slab
     for (int sa = 8; sa >= 2; --sa) {
       if (force_sa > 0 && sa != force_sa) continue;
       const size_t need = arcq::ws_smem_layout(best_bn, ws, sa, bits, G, stationary != 0, dense).total;

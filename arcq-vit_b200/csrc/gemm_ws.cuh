@@ -60,6 +60,13 @@ __host__ __device__ constexpr int raw_row_bytes(int bits) { return raw_groups(bi
 __host__ __device__ constexpr uint32_t raw_slot_size(int bn, int bits) {
   return (static_cast<uint32_t>(bn) * raw_row_bytes(bits) + 16 + 127) & ~127u;   // +16: 3-bit reads may look 3 bytes ahead
 }
+// Narrow stationary slabs (few rows: small batches, where one CTA's latency chain is the whole kernel) take
+// all their packed codes in one burst -- every raw load issued at once on one barrier -- and rebuild all the
+// sub-tiles in one pass with one hand-over, instead of one load / rebuild / hand-over round per sub-tile.
+__host__ __device__ constexpr int raw_loads(int G, int bits) { return (G + raw_groups(bits) - 1) / raw_groups(bits); }
+__host__ __device__ constexpr bool ws_burst(int bn, int bits, int G, bool stationary, bool dense) {
+  return stationary && !dense && raw_loads(G, bits) * raw_slot_size(bn, bits) <= 16384u;
+}
 
 struct WsSmem {
   // offsets from the 1024-aligned base
@@ -78,7 +85,9 @@ __host__ __device__ inline WsSmem ws_smem_layout(int bn, int ws, int sa, int bit
   s.a = 0;
   s.w = s.a + static_cast<uint32_t>(sa) * kStageA;
   const uint32_t area = s.w + static_cast<uint32_t>(ws) * bn * 128;
-  const uint32_t raw_bytes = dense ? 0u : kRawSlots * raw_slot_size(bn, bits);
+  const uint32_t raw_bytes = dense ? 0u
+                             : (ws_burst(bn, bits, G, stationary, dense) ? raw_loads(G, bits) : kRawSlots) *
+                                   raw_slot_size(bn, bits);
   const uint32_t fold_bytes = dense ? 0u : (static_cast<uint32_t>(bn) * G * 4u + 127) & ~127u;
   uint32_t area_bytes;
   if (stationary) {
@@ -116,7 +125,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   uint64_t* const bars = reinterpret_cast<uint64_t*>(s_bias + 256);
   uint64_t* const a_full = bars;             // [sa]   <= 8
   uint64_t* const a_empty = bars + 8;        // [sa]
-  uint64_t* const w_full = bars + 16;        // [ws]   <= 16
+  uint64_t* const w_full = bars + 16;        // [ws]   <= 16 (ring) or <= 32 (stationary)
   uint64_t* const w_empty = bars + 32;       // [ws]
   uint64_t* const raw_full = bars + 48;      // [2]
   uint64_t* const raw_empty = bars + 50;     // [2]
@@ -144,17 +153,16 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   const bool stationary = p.stationary != 0;
 
   const bool dense = p.dense != 0;
-  if (tid < 16 && !dense) s_lut[tid] = (tid < (1 << BITS)) ? p.cb_w[tid] : 0.0f;
-  if (tid < 256 && !dense) {
-    const int lo = tid & 15, hi = tid >> 4;
-    __half2 v = __floats2half2_rn(lo < (1 << BITS) ? p.cb_w[lo] : 0.0f, hi < (1 << BITS) ? p.cb_w[hi] : 0.0f);
-#pragma unroll
-    for (int c = 0; c < kLutCopies; ++c) s_lut2[tid * kLutCopies + c] = *reinterpret_cast<uint32_t*>(&v);
-  }
-  for (int i = tid; i < bn; i += kWsThreads) s_bias[i] = (p.bias != nullptr) ? p.bias[n0 + i] : 0.0f;
+  const bool burst = ws_burst(p.bn, BITS, p.G, p.stationary != 0, dense);
+  // Only the barriers and the tensor-memory allocation are set up before the roles part: the pair table and
+  // the bias are filled by the roles that read them (builders, epilogue), so their global-memory latency does
+  // not hold back the first TMA loads.
   if (tid == 0) {
     for (int i = 0; i < p.sa; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
-    for (int i = 0; i < p.ws; ++i) { mbar_init(&w_full[i], dense ? 1 : kWsProducerWarps); mbar_init(&w_empty[i], 1); }
+    // a stationary slab never recycles a slot: its (up to 32) full barriers may run into the empty ones' space
+    for (int i = 0; i < p.ws; ++i) mbar_init(&w_full[i], dense ? 1 : kWsProducerWarps);
+    if (p.stationary == 0)
+      for (int i = 0; i < p.ws; ++i) mbar_init(&w_empty[i], 1);
     for (int i = 0; i < kRawSlots; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kWsProducerWarps); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
     mbar_fence_init();
@@ -207,6 +215,16 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
               w_ph ^= wrap ? 1u : 0u;
             }
           }
+        } else if (burst) {
+          if (b0 == 0 && g == 0) {
+            if (lane == 0) {
+              const int n_loads = raw_loads(G, BITS);
+              mbar_arrive_expect_tx(&raw_full[0], static_cast<uint32_t>(n_loads) * bn * raw_row_bytes(BITS));
+              for (int q = 0; q < n_loads; ++q)
+                tma_load_2d(sRaw + q * raw_slot_bytes, &tm_w, &raw_full[0], q * raw_x_step, n0);
+            }
+            __syncwarp();
+          }
         } else if ((!stationary || b0 == 0) && (g % RG) == 0) {
           ok = ok && mbar_wait_relaxed(&raw_empty[r_slot], r_ph);
           if (lane == 0 && ok) {
@@ -258,7 +276,13 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
       }
       tc_fence_after_sync();
       if (lane == 0) stamp(8 + 2 * batch);
-      const bool w_waits = !stationary || b0 == 0;   // a stationary slab is built once
+      bool w_waits = !stationary || b0 == 0;   // a stationary slab is built once
+      if (burst && b0 == 0) {
+        // a slab built in one burst hands all its sub-tiles over together: take them all now (nothing the
+        // builders wait for depends on the MMAs), so that even the first tile runs the lean loop below
+        for (int g = 0; g < G; ++g) ok = ok && mbar_wait_relaxed(&w_full[g], 0u, 32);
+        w_waits = false;
+      }
       const bool st = tr != nullptr && batch == 2 && lane == 0;
       const uint32_t leader = lane == 0 ? 1u : 0u;
       if (!w_waits && nb == 1) {
@@ -323,6 +347,8 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
     if (!ok && lane == 0) atomicExch(p.status, kStatusWsTimeout);
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue
+    for (int i = tid - 2 * 32; i < bn; i += 4 * 32) s_bias[i] = (p.bias != nullptr) ? __ldg(p.bias + n0 + i) : 0.0f;
+    asm volatile("bar.sync 2, 128;" ::: "memory");   // the four epilogue warps
     const int lq = warp & 3;  // tensor-memory lane quarter this warp may read
     uint32_t tile_seq = 0;
     for (int t = 0; t < my_tiles && ok; ++t, ++tile_seq) {
@@ -444,6 +470,13 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
     // (W-stationary), else from global memory (L2 after the first walk of the slab).
     const int chunk = ptid & 7;
     const int units = (bn * 8 + kWsProducerThreads - 1 - ptid) / kWsProducerThreads;
+    // pair table: codebook values of (low nibble, high nibble) of a byte, kLutCopies copies side by side
+    if (my_tiles > 0 && !dense) {
+      const int lo = ptid & 15, hi = ptid >> 4;
+      __half2 v = __floats2half2_rn(lo < (1 << BITS) ? __ldg(p.cb_w + lo) : 0.0f, hi < (1 << BITS) ? __ldg(p.cb_w + hi) : 0.0f);
+#pragma unroll
+      for (int c = 0; c < kLutCopies; ++c) s_lut2[ptid * kLutCopies + c] = *reinterpret_cast<uint32_t*>(&v);
+    }
     // fold the slab's statistics once: (sigma, mu') as one half2 word per (row, group)
     if (my_tiles > 0 && !dense) {
       for (int i = ptid; i < bn * G; i += kWsProducerThreads) {
@@ -454,8 +487,48 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kWsProducerThreads) : "memory");   // producer warps only
     }
+    if (burst && my_tiles > 0) {
+      // every (sub-tile, row, chunk) unit of the slab in one strided pass, then one hand-over per sub-tile
+      ok = mbar_wait_relaxed(&raw_full[0], 0u);
+      const int per_g = bn * 8;
+      int g = 0, idx = ptid;
+      while (ok) {
+        while (idx >= per_g) { idx -= per_g; ++g; }
+        if (g >= G) break;
+        const int r = idx >> 3, ch = idx & 7;
+        const uint8_t* rp = sRaw + (g / RG) * raw_slot_bytes + (g % RG) * (8 * BITS) + r * raw_row_bytes(BITS);
+        uint32_t w;
+        if (BITS == 4) {
+          w = *reinterpret_cast<const uint32_t*>(rp + 4 * ch);
+        } else if (BITS == 3) {
+          const int off = 3 * ch, al = off & ~3, sh = (off & 3) * 8;
+          w = spread_3_to_nibbles(__funnelshift_r(*reinterpret_cast<const uint32_t*>(rp + al),
+                                                  *reinterpret_cast<const uint32_t*>(rp + al + 4), sh) & 0xFFFFFFu);
+        } else {
+          w = spread_2_to_nibbles(*reinterpret_cast<const uint16_t*>(rp + 2 * ch));
+        }
+        const uint32_t fw = s_fold[r * G + g];
+        const __half2 f2 = *reinterpret_cast<const __half2*>(&fw);
+        const __half2 s2 = __low2half2(f2);
+        const __half2 m2 = __high2half2(f2);
+        uint32_t hv[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t pv = s_lut2[((w >> (8 * q)) & 0xFFu) * kLutCopies + (lane & (kLutCopies - 1))];
+          const __half2 r2 = __hfma2(s2, *reinterpret_cast<const __half2*>(&pv), m2);
+          hv[q] = *reinterpret_cast<const uint32_t*>(&r2);
+        }
+        *reinterpret_cast<uint4*>(sW + g * bn * 128 + sw128_offset(r, ch)) = make_uint4(hv[0], hv[1], hv[2], hv[3]);
+        idx += kWsProducerThreads;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0)
+        for (int gg = 0; gg < G; ++gg) mbar_arrive(&w_full[gg]);
+      if (ptid == 0) stamp(7);
+    }
     for (int f = 0; f < fills && ok; ++f) {
-      if (my_tiles == 0 || dense) break;
+      if (my_tiles == 0 || dense || burst) break;
       for (int g = 0; g < G && ok; ++g) {
         const uint32_t rslot = r_slot;
         if ((g % RG) == 0) ok = mbar_wait_relaxed(&raw_full[rslot], r_ph);
