@@ -15,7 +15,7 @@ DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 
 # every symbol include/arcq_b200.h declares
 EXPORTS = (
-    "arcq_version", "arcq_last_error_string", "arcq_device_status", "arcq_debug_trace", "arcq_act_quant", "arcq_gelu_act_quant", "arcq_packed_gemm", "arcq_packed_weight_gemm", "arcq_dense_weight_gemm", "arcq_packed_linear_static_scratch", "arcq_add_layernorm",
+    "arcq_version", "arcq_last_error_string", "arcq_device_status", "arcq_debug_trace", "arcq_debug_set_option", "arcq_debug_get_option", "arcq_debug_wait_timeout", "arcq_act_quant", "arcq_gelu_act_quant", "arcq_packed_gemm", "arcq_packed_weight_gemm", "arcq_dense_weight_gemm", "arcq_packed_linear_static_scratch", "arcq_add_layernorm",
     "arcq_unpack_codes", "arcq_pack_codes", "arcq_dequant",
 )
 
@@ -41,6 +41,9 @@ def load() -> ctypes.CDLL:
     lib.arcq_last_error_string.restype = ctypes.c_char_p
     lib.arcq_device_status.restype = ci
     lib.arcq_debug_trace.argtypes = [vp]
+    lib.arcq_debug_set_option.argtypes = [ctypes.c_char_p, ci]
+    lib.arcq_debug_get_option.argtypes = [ctypes.c_char_p, ctypes.POINTER(ci)]
+    lib.arcq_debug_wait_timeout.argtypes = [ctypes.c_uint, vp]
     lib.arcq_act_quant.argtypes = [vp, ci, i64, i64, vp, vp, ci, ci, vp, vp, vp, vp, vp, ci, vp]
     lib.arcq_gelu_act_quant.argtypes = lib.arcq_act_quant.argtypes
     lib.arcq_packed_gemm.argtypes = [vp] * 11 + [ci, ci, i64, i64, i64, vp, ci, vp]
@@ -59,3 +62,32 @@ def load() -> ctypes.CDLL:
 
 def last_error() -> str:
     return load().arcq_last_error_string().decode("utf-8", "replace")
+
+
+def set_option(name: str, value: int) -> None:
+    """Override one tuning option of the library (see ``arcq_debug_set_option`` in the header)."""
+    if load().arcq_debug_set_option(name.encode(), int(value)) != 0:
+        raise ValueError(last_error())
+
+
+def get_option(name: str) -> int:
+    v = ctypes.c_int(0)
+    if load().arcq_debug_get_option(name.encode(), ctypes.byref(v)) != 0:
+        raise ValueError(last_error())
+    return int(v.value)
+
+
+class option:
+    """``with option("ARCQ_ACT_QUANT_V1", 1): ...`` -- set a tuning option for a block, then restore it."""
+
+    def __init__(self, name: str, value: int):
+        self.name, self.value = name, value
+
+    def __enter__(self):
+        self.old = get_option(self.name)
+        set_option(self.name, self.value)
+        return self
+
+    def __exit__(self, *exc):
+        set_option(self.name, self.old)
+        return False

@@ -116,6 +116,9 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const T* __restrict__ x,
                                                         uint8_t* __restrict__ packed, float* __restrict__ mu_out,
                                                         float* __restrict__ sigma_out,
                                                         float* __restrict__ codesum_out, XH* __restrict__ xhat) {
+  pdl_launch_dependents();   // the next kernel of the stream may start its set-up
+  pdl_wait();                // the input may be the previous kernel's output
+
   constexpr int L = 1 << BITS;
   __shared__ float s_th[16];
   __shared__ float s_cb[16];

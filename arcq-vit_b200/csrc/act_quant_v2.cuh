@@ -121,6 +121,9 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
                                                                    float* __restrict__ sigma_out,
                                                                    float* __restrict__ codesum_out,
                                                                    XH* __restrict__ xhat) {
+  pdl_launch_dependents();   // the next kernel of the stream may start its set-up
+  pdl_wait();                // the input may be the previous kernel's output
+
   constexpr int L = 1 << BITS;
   constexpr int kPitch = Aq2Row<T>::kPitch, kRowBytes = Aq2Row<T>::kBytes;
   constexpr int kChunksPerRow = kRowBytes / 16;

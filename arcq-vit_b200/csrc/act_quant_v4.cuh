@@ -63,6 +63,9 @@ __global__ void __launch_bounds__(kAq4Threads, 4) act_quant_v4_kernel(const T* _
                                                                    float* __restrict__ sigma_out,
                                                                    float* __restrict__ codesum_out,
                                                                    T* __restrict__ xhat) {
+  pdl_launch_dependents();   // the next kernel of the stream may start its set-up
+  pdl_wait();                // the input may be the previous kernel's output
+
   static_assert(sizeof(T) == 2, "two-lane kernel is written for 16-bit element types");
   constexpr int L = 1 << BITS;
   constexpr int kPitch = Aq2Row<T>::kPitch, kRowBytes = Aq2Row<T>::kBytes;   // 144, 128

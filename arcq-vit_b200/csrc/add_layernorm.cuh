@@ -15,6 +15,9 @@ __global__ void __launch_bounds__(256) add_layernorm_kernel(const __half* __rest
                                                             const float* __restrict__ gamma,
                                                             const float* __restrict__ beta, float eps, long long M, int K,
                                                             __half* __restrict__ sum_out, __half* __restrict__ h_out) {
+  pdl_launch_dependents();   // the next kernel of the stream may start its set-up
+  pdl_wait();                // the input may be the previous kernel's output
+
   const int lane = threadIdx.x & 31;
   const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
   const int chunks = K >> 3;
@@ -104,6 +107,9 @@ __global__ void __launch_bounds__(256) add_layernorm_rows_kernel(const __half* _
                                                                  const float* __restrict__ beta, float eps,
                                                                  long long M, __half* __restrict__ sum_out,
                                                                  __half* __restrict__ h_out) {
+  pdl_launch_dependents();   // the next kernel of the stream may start its set-up
+  pdl_wait();                // the input may be the previous kernel's output
+
   constexpr int K = LANES * 24, kRowsPerWarp = 32 / LANES;
   const int lane = threadIdx.x & 31, l = lane % LANES, sub = lane / LANES;
   float gg[3][8], bb[3][8];

@@ -8,6 +8,7 @@
 #include <stdio.h>
 #include <stdarg.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "../../include/arcq_b200.h"
 #include "ptx.cuh"
@@ -17,6 +18,7 @@
 #include "codes.cuh"
 #include "packed_gemm.cuh"
 #include "gemm_ws.cuh"
+#include "gemm_pair.cuh"
 #include "add_layernorm.cuh"
 #include <cudaTypedefs.h>
 
@@ -66,12 +68,56 @@ int sm_count() {
   return sms;
 }
 
-// Tuning overrides for experiments (unset in normal use): ARCQ_WS_BN, ARCQ_WS_SA, ARCQ_WS_WS,
-// ARCQ_WS_STATIONARY, ARCQ_WS_NBB, ARCQ_WS_GRID,
-// ARCQ_WS_TMA_STORE, ARCQ_WS_ROTATE, ARCQ_ACT_QUANT_V1, ARCQ_ACT_QUANT_V2, ARCQ_LN_PLAIN.
-int env_int(const char* name, int dflt) {
-  const char* v = getenv(name);
-  return (v != nullptr && *v != 0) ? atoi(v) : dflt;
+// Tuning options.  Each has a built-in default; an environment variable of the same name, read once when the
+// library is first used, or arcq_debug_set_option() at any time, overrides it.  Normal use sets none of them.
+enum Opt {
+  O_WS_BN, O_WS_SA, O_WS_WS, O_WS_STATIONARY, O_WS_NBB, O_WS_GRID, O_WS_TMA_STORE, O_WS_ROTATE,
+  O_ACT_QUANT_V1, O_ACT_QUANT_V2, O_LN_PLAIN,
+  O_PAIR, O_PAIR_MIN_M, O_PAIR_BN, O_PAIR_SA, O_PAIR_KS, O_PAIR_NBB, O_PAIR_LUT, O_PAIR_PAIRS, O_PAIR_STATIONARY,
+  O_PAIR_WS, O_PAIR_FLAGS, O_PDL, O_POLL_LIMIT, O_SPIN_LIMIT, O_COUNT
+};
+struct OptDef { const char* name; int dflt; };
+const OptDef kOptDefs[O_COUNT] = {
+    {"ARCQ_WS_BN", 0},        {"ARCQ_WS_SA", 0},          {"ARCQ_WS_WS", 0},       {"ARCQ_WS_STATIONARY", -1},
+    {"ARCQ_WS_NBB", 0},       {"ARCQ_WS_GRID", 0},        {"ARCQ_WS_TMA_STORE", 1}, {"ARCQ_WS_ROTATE", 1},
+    {"ARCQ_ACT_QUANT_V1", 0}, {"ARCQ_ACT_QUANT_V2", 0},   {"ARCQ_LN_PLAIN", 0},
+    {"ARCQ_PAIR", 1},         {"ARCQ_PAIR_MIN_M", 1024},  {"ARCQ_PAIR_BN", 0},     {"ARCQ_PAIR_SA", 0},
+    {"ARCQ_PAIR_KS", 0},      {"ARCQ_PAIR_NBB", 0},       {"ARCQ_PAIR_LUT", 0},    {"ARCQ_PAIR_PAIRS", 0},
+    {"ARCQ_PAIR_STATIONARY", -1}, {"ARCQ_PAIR_WS", 0}, {"ARCQ_PAIR_FLAGS", 0}, {"ARCQ_PDL", 1},
+    {"ARCQ_POLL_LIMIT", 1 << 21}, {"ARCQ_SPIN_LIMIT", 1 << 25},
+};
+int g_opt[O_COUNT];
+void load_options() {
+  static const bool once = [] {
+    for (int i = 0; i < O_COUNT; ++i) {
+      const char* v = getenv(kOptDefs[i].name);
+      g_opt[i] = (v != nullptr && *v != 0) ? atoi(v) : kOptDefs[i].dflt;
+    }
+    return true;
+  }();
+  (void)once;
+}
+int opt(Opt o) {
+  load_options();
+  return g_opt[o];
+}
+
+// Launch as a programmatic dependent of the kernel before it in the stream (unless ARCQ_PDL is 0): the grid may
+// become resident while that kernel drains; every kernel launched this way calls pdl_wait() before it reads
+// anything a predecessor writes.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = grid;
+  lc.blockDim = block;
+  lc.dynamicSmemBytes = smem;
+  lc.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = attr;
+  lc.numAttrs = opt(O_PDL) != 0 ? 1 : 0;
+  return cudaLaunchKernelEx(&lc, kernel, static_cast<KArgs>(args)...);
 }
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
@@ -89,16 +135,13 @@ cudaError_t launch_act_quant(const void* x, long long groups, const float* th, c
   const int grid = grid_for((groups + 3) / 4, 8, 8);
   const T* xt = static_cast<const T*>(x);
   if (xhat == nullptr) {
-    arcq::act_quant_kernel<T, BITS, float, false, PRE><<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, nullptr);
+    launch_pdl(arcq::act_quant_kernel<T, BITS, float, false, PRE>, grid, 256, 0, st, xt, groups, th, cb, packed, mu, sg, cs, static_cast<float*>(nullptr));
   } else if (xhat_dtype == ARCQ_DT_F32) {
-    arcq::act_quant_kernel<T, BITS, float, true, PRE>
-        <<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, static_cast<float*>(xhat));
+    launch_pdl(arcq::act_quant_kernel<T, BITS, float, true, PRE>, grid, 256, 0, st, xt, groups, th, cb, packed, mu, sg, cs, static_cast<float*>(xhat));
   } else if (xhat_dtype == ARCQ_DT_F16) {
-    arcq::act_quant_kernel<T, BITS, __half, true, PRE>
-        <<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, static_cast<__half*>(xhat));
+    launch_pdl(arcq::act_quant_kernel<T, BITS, __half, true, PRE>, grid, 256, 0, st, xt, groups, th, cb, packed, mu, sg, cs, static_cast<__half*>(xhat));
   } else {
-    arcq::act_quant_kernel<T, BITS, __nv_bfloat16, true, PRE>
-        <<<grid, 256, 0, st>>>(xt, groups, th, cb, packed, mu, sg, cs, static_cast<__nv_bfloat16*>(xhat));
+    launch_pdl(arcq::act_quant_kernel<T, BITS, __nv_bfloat16, true, PRE>, grid, 256, 0, st, xt, groups, th, cb, packed, mu, sg, cs, static_cast<__nv_bfloat16*>(xhat));
   }
   return cudaGetLastError();
 }
@@ -118,17 +161,17 @@ cudaError_t launch_act_quant_v2(const void* x, long long groups, const float* th
     auto k = arcq::act_quant_v2_kernel<T, BITS, T, false, PRE>;
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    k<<<grid, arcq::kAq2Threads, smem, st>>>(xt, groups, th, cb, packed, mu, sg, cs, nullptr);
+    launch_pdl(k, grid, arcq::kAq2Threads, smem, st, xt, groups, th, cb, packed, mu, sg, cs, static_cast<T*>(nullptr));
   } else if (packed == nullptr) {
     auto k = arcq::act_quant_v2_kernel<T, BITS, T, true, PRE, false>;
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    k<<<grid, arcq::kAq2Threads, smem, st>>>(xt, groups, th, cb, nullptr, mu, sg, cs, static_cast<T*>(xhat));
+    launch_pdl(k, grid, arcq::kAq2Threads, smem, st, xt, groups, th, cb, static_cast<uint8_t*>(nullptr), mu, sg, cs, static_cast<T*>(xhat));
   } else {
     auto k = arcq::act_quant_v2_kernel<T, BITS, T, true, PRE>;
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    k<<<grid, arcq::kAq2Threads, smem, st>>>(xt, groups, th, cb, packed, mu, sg, cs, static_cast<T*>(xhat));
+    launch_pdl(k, grid, arcq::kAq2Threads, smem, st, xt, groups, th, cb, packed, mu, sg, cs, static_cast<T*>(xhat));
   }
   return cudaGetLastError();
 }
@@ -149,7 +192,7 @@ cudaError_t launch_act_quant_v4(const void* x, long long groups, const float* th
     auto k = arcq::act_quant_v4_kernel<T, BITS, WX, PRE, WP>;                                                    \
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));            \
     if (e != cudaSuccess) return e;                                                                              \
-    k<<<grid, arcq::kAq4Threads, smem, st>>>(xt, groups, th, cb, packed, mu, sg, cs, xo);                        \
+    launch_pdl(k, grid, arcq::kAq4Threads, smem, st, xt, groups, th, cb, packed, mu, sg, cs, xo);                  \
   } while (0)
   if (xhat == nullptr) ARCQ_AQ4(false, true);
   else if (packed == nullptr) ARCQ_AQ4(true, false);
@@ -176,14 +219,14 @@ cudaError_t dispatch_act_quant_bits(int bits, const void* x, int x_dtype, long l
   // The one-thread-per-group kernel needs enough groups to fill the machine (148 SMs x 4 blocks x 128
   // threads); below that the 8-lanes-per-group kernel has 8 times the parallelism and lower latency.
   const bool enough = groups >= static_cast<long long>(sm_count()) * 4 * arcq::kAq2Threads / 2;
-  const bool v2 = enough && env_int("ARCQ_ACT_QUANT_V1", 0) == 0 && aligned(x, 16) &&
+  const bool v2 = enough && opt(O_ACT_QUANT_V1) == 0 && aligned(x, 16) &&
                   (packed == nullptr || aligned(packed, 16)) &&
                   (xhat == nullptr || (xhat_dtype == x_dtype && aligned(xhat, 16)));
   if (v2) {
     // The two-lanes-per-group form (16-bit inputs) measured faster only where the per-element arithmetic is
     // long, i.e. with the fused GELU (42 vs 48 us on [12608,1536]); the plain quantizer stays one thread per
     // group (9.3 vs 10.8 us on [12608,384]).  ARCQ_ACT_QUANT_V2 = 1 / 2 forces the one-lane / two-lane form.
-    const int force = env_int("ARCQ_ACT_QUANT_V2", 0);
+    const int force = opt(O_ACT_QUANT_V2);
     const bool two_lane = force == 2 || (force == 0 && PRE == 1);
     switch (bits) {
       case 4: return launch_staged<T, 4, PRE>(two_lane, x, groups, th, cb, packed, mu, sg, cs, xhat, st);
@@ -218,30 +261,56 @@ int choose_bn(long long M, long long N) {
 
 // ---- tensor maps (driver entry point fetched through the runtime, so libcuda is not linked) ----
 PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  static const PFN_cuTensorMapEncodeTiled_v12000 fn = [] {   // resolved once; the initialisation is thread-safe
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
-  }
+      return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    return static_cast<PFN_cuTensorMapEncodeTiled_v12000>(nullptr);
+  }();
   return fn;
 }
 
-// 2-D row-major tensor [rows, cols] of `elem_bytes`-byte elements, box [box_cols x box_rows].
+// 2-D row-major tensor [rows, cols] of `elem_bytes`-byte elements, box [box_cols x box_rows].  A descriptor
+// depends only on these values (not on what the memory holds), so the last few are kept per host thread:
+// a model's layers present the same (pointer, shape) again on every forward.
+struct TensorMapKey {
+  const void* base;
+  uint64_t rows, cols;
+  uint32_t box_cols, box_rows;
+  int dt, swz;
+  bool operator==(const TensorMapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && box_cols == o.box_cols && box_rows == o.box_rows &&
+           dt == o.dt && swz == o.swz;
+  }
+};
 bool make_tensor_map_2d(CUtensorMap* tm, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows,
                         uint64_t cols, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swz) {
+  constexpr int kSlots = 256;
+  struct Slot { TensorMapKey key; CUtensorMap map; bool used; };
+  static thread_local Slot cache[kSlots] = {};
+  const TensorMapKey key{base, rows, cols, box_cols, box_rows, static_cast<int>(dt), static_cast<int>(swz)};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+  h = (h ^ (rows * 0x9E3779B97F4A7C15ull) ^ (cols << 7) ^ (static_cast<uint64_t>(box_rows) << 29) ^ (static_cast<uint64_t>(box_cols) << 41)) * 0xD6E8FEB86659FD93ull;
+  Slot& slot = cache[(h >> 40) % kSlots];
+  if (slot.used && slot.key == key) {
+    *tm = slot.map;
+    return true;
+  }
   PFN_cuTensorMapEncodeTiled_v12000 enc = tensor_map_encoder();
   if (enc == nullptr) return false;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * static_cast<uint64_t>(elem_bytes)};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  return enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
-             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  slot.key = key;
+  slot.map = *tm;
+  slot.used = true;
+  return true;
 }
 
 struct WsConfig {
@@ -270,17 +339,17 @@ bool choose_ws_config(long long M, long long N, long long K, int bits, bool dens
     if (ctas * 4 >= 3LL * sms) { best_bn = bn; best_ctas = ctas; break; }  // first (widest) that fills 3/4 of the SMs
     if (ctas > best_ctas) { best_ctas = ctas; best_bn = bn; }
   }
-  const int force_bn = env_int("ARCQ_WS_BN", 0);
+  const int force_bn = opt(O_WS_BN);
   if (force_bn > 0 && force_bn % 16 == 0 && force_bn <= 256 && N % force_bn == 0) best_bn = force_bn;
   if (best_bn == 0) return false;
   c->bn = best_bn;
   const long long slabs = N / best_bn;
   const long long per = sms / slabs;
   c->grid = static_cast<int>(slabs * (tiles_m < per ? tiles_m : per));
-  const int force_grid = env_int("ARCQ_WS_GRID", 0);
+  const int force_grid = opt(O_WS_GRID);
   if (force_grid > 0 && force_grid <= sms) c->grid = force_grid;
-  const int force_stat = env_int("ARCQ_WS_STATIONARY", -1), force_sa = env_int("ARCQ_WS_SA", 0);
-  const int force_ws = env_int("ARCQ_WS_WS", 0), force_nbb = env_int("ARCQ_WS_NBB", 0);
+  const int force_stat = opt(O_WS_STATIONARY), force_sa = opt(O_WS_SA);
+  const int force_ws = opt(O_WS_WS), force_nbb = opt(O_WS_NBB);
   // stationary if all G sub-tiles plus two A stages fit
   for (int stationary = 1; stationary >= 0; --stationary) {
     if (force_stat >= 0 && stationary != force_stat) continue;
@@ -303,6 +372,160 @@ bool choose_ws_config(long long M, long long N, long long K, int bits, bool dens
   return false;
 }
 
+
+// A one-CTA kernel whose only job is to let a bounded wait run out: it initialises an mbarrier that nothing
+// ever arrives on, waits for it with the given poll limit, and leaves kStatusDebugTimeout in the status word.
+// Exercises the error path of the kernels' waits (status set, kernel returns) without hanging anything.
+constexpr int kStatusDebugTimeout = 0x7E57;
+__global__ void debug_wait_timeout_kernel(uint32_t poll_limit, int* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    arcq::mbar_init(&bar, 1);
+    arcq::mbar_fence_init();
+  }
+  __syncthreads();
+  const bool ok = arcq::mbar_wait_sleep_a(arcq::smem_u32(&bar), 0u, poll_limit, 32);
+  if (!ok && threadIdx.x == 0) atomicExch(status, kStatusDebugTimeout);
+}
+
+// ---- CTA-pair kernel: configuration ----
+struct PairConfig {
+  int bn, ws, sa, ks, nbb, stationary, lut_shift, pairs;
+  size_t smem;
+};
+
+// How many two-CTA clusters of the pair kernel can be resident at once (each takes two whole SMs).
+int max_resident_pairs(int bits, size_t smem) {
+  static thread_local int cached_dev = -1, cached = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev == cached_dev && cached > 0) return cached;
+  int n = 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(sm_count() / 2 * 2));
+  cfg.blockDim = dim3(arcq::kPairThreads);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaErrorUnknown;
+  if (bits == 4) e = cudaOccupancyMaxActiveClusters(&n, arcq::packed_weight_gemm_pair_kernel<4>, &cfg);
+  else if (bits == 3) e = cudaOccupancyMaxActiveClusters(&n, arcq::packed_weight_gemm_pair_kernel<3>, &cfg);
+  else e = cudaOccupancyMaxActiveClusters(&n, arcq::packed_weight_gemm_pair_kernel<2>, &cfg);
+  if (e != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    n = sm_count() / 2;
+  }
+  if (n > sm_count() / 2) n = sm_count() / 2;
+  cached = n;
+  cached_dev = dev;
+  return n;
+}
+
+template <int B>
+cudaError_t pair_set_smem(size_t smem) {
+  return cudaFuncSetAttribute(arcq::packed_weight_gemm_pair_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(smem));
+}
+
+// Slab width, stages and grid for the CTA-pair kernel; false when the shape is left to the one-CTA kernel
+// (small M, N without a slab width that is a multiple of 32, ...).  The cost model counts tensor-pipe
+// cycles per SM: a 256 x bn x 64 stage is four instructions of bn/2 cycles each; rebuilding one
+// [bn/2 x 64] sub-tile costs about 300 + 6.5 * bn/2 cycles on the eight producer warps.
+bool choose_pair_config(long long M, long long N, long long K, int bits, bool y_f32, PairConfig* c) {
+  if (opt(O_PAIR) == 0 || M < opt(O_PAIR_MIN_M)) return false;
+  const int G = static_cast<int>(K / 64);
+  if (G < 1 || G > 64) return false;
+  const long long tiles_m = (M + arcq::kPairTileM - 1) / arcq::kPairTileM;
+  const size_t full_smem = kSmemBudget + 1024;
+  {
+    // raise the kernel's dynamic shared-memory ceiling once per (host thread, device, code width)
+    static thread_local int done_dev[5] = {-1, -1, -1, -1, -1};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (done_dev[bits] != dev) {
+      if (bits == 4 ? pair_set_smem<4>(full_smem) != cudaSuccess
+                    : bits == 3 ? pair_set_smem<3>(full_smem) != cudaSuccess : pair_set_smem<2>(full_smem) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+      }
+      done_dev[bits] = dev;
+    }
+  }
+  int max_pairs = max_resident_pairs(bits, full_smem);
+  if (opt(O_PAIR_PAIRS) > 0 && opt(O_PAIR_PAIRS) < max_pairs) max_pairs = opt(O_PAIR_PAIRS);
+  static const int cand[] = {192, 160, 128, 96, 64, 32};     // at most arcq::kPairMaxBn
+  double best_cost = 0;
+  bool found = false;
+  PairConfig best = {};
+  for (int bn : cand) {
+    if (N % bn != 0) continue;
+    if (opt(O_PAIR_BN) > 0 && bn != opt(O_PAIR_BN)) continue;
+    const long long slabs = N / bn;
+    if (slabs > max_pairs) continue;
+    const int hb = bn / 2;
+    long long per = max_pairs / slabs;
+    if (per > tiles_m) per = tiles_m;
+    const long long tiles_pp = (tiles_m + per - 1) / per;
+    // Cost model in microseconds, constants from time stamps taken inside the kernel on the DeiT shapes: a tile is
+    // bound by its output stores (about 22 GB/s per SM) or by the issuing thread (about 110 cycles per
+    // instruction plus 0.15 us per stage); a sub-tile rebuild takes 0.12 + 0.0026 * rows us when both warp
+    // groups build (stationary slab) and about twice that when only the weight warps do (streaming ring).
+    const int esize = y_f32 ? 4 : 2;
+    const double t_write = 128.0 * bn * esize / 22.0e3;
+    const double t_l2 = static_cast<double>(slabs) * M * K * 2.0 / 5.0e6;    // every slab streams the whole activation
+    for (int stationary = 1; stationary >= 0; --stationary) {
+      if (opt(O_PAIR_STATIONARY) >= 0 && stationary != opt(O_PAIR_STATIONARY)) continue;
+      PairConfig k = {};
+      k.bn = bn; k.stationary = stationary; k.pairs = static_cast<int>(slabs * per);
+      k.nbb = stationary ? 1 : 2;
+      if (opt(O_PAIR_NBB) == 1 || opt(O_PAIR_NBB) == 2) k.nbb = opt(O_PAIR_NBB);
+      // two 64-wide sub-tiles per stage: one wait and one pair of commits per eight instructions keeps the
+      // issuing thread ahead of the tensor pipe
+      k.ks = (G % 2 == 0) ? 2 : (G % 3 == 0) ? 3 : 1;
+      if (opt(O_PAIR_KS) > 0 && G % opt(O_PAIR_KS) == 0) k.ks = opt(O_PAIR_KS);
+      k.ws = stationary ? G : (opt(O_PAIR_WS) > 0 ? opt(O_PAIR_WS) : 4);
+      if (!stationary && k.ws > G) k.ws = G;
+      if (k.ws > (stationary ? 32 : 16) || k.ws < k.ks || (!stationary && k.ws % k.ks != 0)) continue;
+      // eight copies of the pair table (more did not measure faster); as many A stages as fit, eight sub-stages at most
+      bool fits = false;
+      for (int lut = (opt(O_PAIR_LUT) > 0 ? opt(O_PAIR_LUT) : 3); lut >= 3 && !fits; --lut) {
+        for (int sa = 8; sa >= 2 && !fits; --sa) {
+          if (opt(O_PAIR_SA) > 0 && sa != opt(O_PAIR_SA)) continue;
+          if (sa * k.ks > 8 && opt(O_PAIR_SA) == 0) continue;            // eight 16 KB sub-stages are plenty
+          const size_t need = arcq::pair_smem_layout(bn, k.ws, sa, k.ks, G, stationary != 0, lut).total;
+          if (need <= kSmemBudget) {
+            k.sa = sa; k.lut_shift = lut; k.smem = need + 1024; fits = true;
+          }
+        }
+        if (opt(O_PAIR_LUT) > 0) break;
+      }
+      if (!fits) continue;
+      const double t_issue = (G / k.ks) * (k.ks * 4 * 0.056 + 0.15);
+      double cost;
+      if (stationary) {
+        const double t_tile = (t_write > t_issue ? t_write : t_issue) + 0.15;
+        const double path = G * (0.12 + 0.0026 * hb) + tiles_pp * t_tile;
+        cost = 2.2 + (path > t_l2 ? path : t_l2);
+      } else {
+        double path = 0;
+        for (long long t = 0; t < tiles_pp; t += k.nbb) {
+          const long long nb = (tiles_pp - t) < k.nbb ? (tiles_pp - t) : k.nbb;
+          const double build = G * (0.25 + 0.0055 * hb), issue = nb * t_issue;
+          path += (build > issue ? build : issue) * 1.2 + nb * (t_write + 0.15);
+        }
+        cost = 2.2 + (path > t_l2 ? path : t_l2);
+      }
+      if (!found || cost < best_cost) { best = k; best_cost = cost; found = true; }
+    }
+  }
+  if (!found) return false;
+  *c = best;
+  return true;
+}
+
 }  // namespace
 
 extern "C" {
@@ -313,6 +536,40 @@ const char* arcq_last_error_string(void) { return g_err; }
 
 int arcq_debug_trace(void* device_buffer) {
   g_trace_buf = static_cast<long long*>(device_buffer);
+  return ARCQ_OK;
+}
+
+int arcq_debug_set_option(const char* name, int value) {
+  if (name == nullptr) return fail(ARCQ_E_BAD_ARG, "null option name");
+  load_options();
+  for (int i = 0; i < O_COUNT; ++i) {
+    if (strcmp(name, kOptDefs[i].name) == 0) {
+      g_opt[i] = value;
+      return ARCQ_OK;
+    }
+  }
+  return fail(ARCQ_E_BAD_ARG, "unknown option %s", name);
+}
+
+int arcq_debug_get_option(const char* name, int* value_out) {
+  if (name == nullptr || value_out == nullptr) return fail(ARCQ_E_BAD_ARG, "null argument");
+  load_options();
+  for (int i = 0; i < O_COUNT; ++i) {
+    if (strcmp(name, kOptDefs[i].name) == 0) {
+      *value_out = g_opt[i];
+      return ARCQ_OK;
+    }
+  }
+  return fail(ARCQ_E_BAD_ARG, "unknown option %s", name);
+}
+
+int arcq_debug_wait_timeout(unsigned poll_limit, void* stream) {
+  if (poll_limit > (1u << 16)) return fail(ARCQ_E_BAD_ARG, "poll_limit above 65536: this entry point is for short waits");
+  int* st = status_ptr();
+  if (st == nullptr) return fail(ARCQ_E_CUDA, "device status word not reachable");
+  debug_wait_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(poll_limit, st);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "debug_wait_timeout launch");
   return ARCQ_OK;
 }
 
@@ -417,7 +674,7 @@ int arcq_packed_gemm(const uint8_t* packed_x, const float* mu_a, const float* si
     e = cudaFuncSetAttribute(arcq::packed_gemm_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
                              static_cast<int>(smem));                                                        \
     if (e == cudaSuccess) {                                                                                  \
-      arcq::packed_gemm_kernel<B><<<grid, arcq::kGemmThreads, smem, st>>>(p);                                \
+      launch_pdl(arcq::packed_gemm_kernel<B>, grid, arcq::kGemmThreads, smem, st, p);                         \
       e = cudaGetLastError();                                                                                \
     }                                                                                                        \
   } while (0)
@@ -454,7 +711,7 @@ static int launch_ws_gemm(bool dense, const void* xhat, const void* w, const flo
 
   // output tensor map for the TMA-store epilogue: 32-row blocks of 64 bytes (32 fp16 / 16 fp32 columns)
   const int out_cw = (y_dtype == ARCQ_DT_F32) ? 16 : 32;
-  const bool use_tma_store = (cfg.bn % out_cw == 0) && env_int("ARCQ_WS_TMA_STORE", 1) != 0;
+  const bool use_tma_store = (cfg.bn % out_cw == 0) && opt(O_WS_TMA_STORE) != 0;
   CUtensorMap tm_y;
   if (!make_tensor_map_2d(&tm_y, y, (y_dtype == ARCQ_DT_F32) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                           (y_dtype == ARCQ_DT_F32) ? 4 : 2, static_cast<uint64_t>(M), static_cast<uint64_t>(N),
@@ -463,7 +720,7 @@ static int launch_ws_gemm(bool dense, const void* xhat, const void* w, const flo
 
   arcq::WsParams p;
   p.tma_store = use_tma_store ? 1 : 0;
-  p.rotate = env_int("ARCQ_WS_ROTATE", 1);
+  p.rotate = opt(O_WS_ROTATE);
   p.mu_w = mu_w; p.sg_w = sigma_w; p.cs_w = codesum_w; p.cb_w = w_codebook; p.bias = bias; p.y = y;
   p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K); p.G = static_cast<int>(K / 64);
   p.bn = cfg.bn; p.ws = cfg.ws; p.sa = cfg.sa; p.nbb = cfg.nbb; p.stationary = cfg.stationary;
@@ -474,20 +731,64 @@ static int launch_ws_gemm(bool dense, const void* xhat, const void* w, const flo
   if (p.status == nullptr) return fail(ARCQ_E_CUDA, "device status word not reachable");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaSuccess;
-#define ARCQ_LAUNCH_WS(B)                                                                                          \
+#define ARCQ_LAUNCH_WS_T(B, T)                                                                                     \
   do {                                                                                                             \
-    e = cudaFuncSetAttribute(arcq::packed_weight_gemm_ws_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+    e = cudaFuncSetAttribute(arcq::packed_weight_gemm_ws_kernel<B, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                              static_cast<int>(cfg.smem));                                                          \
     if (e == cudaSuccess) {                                                                                        \
-      arcq::packed_weight_gemm_ws_kernel<B><<<cfg.grid, arcq::kWsThreads, cfg.smem, st>>>(tm_a, tm_w, tm_y, p);          \
+      launch_pdl(arcq::packed_weight_gemm_ws_kernel<B, T>, cfg.grid, arcq::kWsThreads, cfg.smem, st, tm_a, tm_w, tm_y, p); \
       e = cudaGetLastError();                                                                                      \
     }                                                                                                              \
+  } while (0)
+  // the instantiation with time stamps runs only while arcq_debug_trace() has a buffer registered
+#define ARCQ_LAUNCH_WS(B)                                                                                          \
+  do {                                                                                                             \
+    if (p.trace != nullptr) ARCQ_LAUNCH_WS_T(B, true);                                                             \
+    else ARCQ_LAUNCH_WS_T(B, false);                                                                               \
   } while (0)
   if (bits == 4) ARCQ_LAUNCH_WS(4);
   else if (bits == 3) ARCQ_LAUNCH_WS(3);
   else ARCQ_LAUNCH_WS(2);
+#undef ARCQ_LAUNCH_WS_T
 #undef ARCQ_LAUNCH_WS
   if (e != cudaSuccess) return cuda_fail(e, "packed_weight_gemm launch");
+  return ARCQ_OK;
+}
+
+// Launch of the CTA-pair kernel (packed weight form only).  Arguments are already validated.
+static int launch_pair_gemm(const PairConfig& cfg, const void* xhat, const void* w, const float* mu_w,
+                            const float* sigma_w, const float* codesum_w, const float* w_codebook, const float* bias,
+                            int bits, int64_t M, int64_t N, int64_t K, void* y, int y_dtype, void* stream) {
+  CUtensorMap tm_a, tm_y;
+  if (!make_tensor_map_2d(&tm_a, xhat, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, static_cast<uint64_t>(M),
+                          static_cast<uint64_t>(K), 64, arcq::kTileM, CU_TENSOR_MAP_SWIZZLE_128B))
+    return fail(ARCQ_E_CUDA, "cuTensorMapEncodeTiled failed for the activation matrix");
+  const int out_cw = (y_dtype == ARCQ_DT_F32) ? 16 : 32;
+  if (!make_tensor_map_2d(&tm_y, y, (y_dtype == ARCQ_DT_F32) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                          (y_dtype == ARCQ_DT_F32) ? 4 : 2, static_cast<uint64_t>(M), static_cast<uint64_t>(N),
+                          out_cw, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+    return fail(ARCQ_E_CUDA, "cuTensorMapEncodeTiled failed for the output matrix");
+  arcq::PairParams p;
+  p.pw = static_cast<const uint8_t*>(w); p.pc = static_cast<int>(K * bits / 8);
+  p.mu_w = mu_w; p.sg_w = sigma_w; p.cs_w = codesum_w; p.cb_w = w_codebook; p.bias = bias; p.y = y;
+  p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K); p.G = static_cast<int>(K / 64);
+  p.bn = cfg.bn; p.ws = cfg.ws; p.sa = cfg.sa; p.ks = cfg.ks; p.nbb = cfg.nbb; p.stationary = cfg.stationary;
+  p.lut_shift = cfg.lut_shift;
+  p.y_f32 = (y_dtype == ARCQ_DT_F32) ? 1 : 0;
+  p.poll_limit = static_cast<uint32_t>(opt(O_POLL_LIMIT));
+  p.spin_limit = static_cast<uint32_t>(opt(O_SPIN_LIMIT));
+  p.trace = g_trace_buf;
+  p.flags = opt(O_PAIR_FLAGS);
+  p.status = status_ptr();
+  if (p.status == nullptr) return fail(ARCQ_E_CUDA, "device status word not reachable");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(2 * cfg.pairs);
+  // the dynamic shared-memory ceiling of the kernel was raised when the configuration was chosen
+  if (bits == 4) launch_pdl(arcq::packed_weight_gemm_pair_kernel<4>, grid, arcq::kPairThreads, cfg.smem, st, tm_a, tm_y, p);
+  else if (bits == 3) launch_pdl(arcq::packed_weight_gemm_pair_kernel<3>, grid, arcq::kPairThreads, cfg.smem, st, tm_a, tm_y, p);
+  else launch_pdl(arcq::packed_weight_gemm_pair_kernel<2>, grid, arcq::kPairThreads, cfg.smem, st, tm_a, tm_y, p);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "packed_weight_gemm (pair) launch");
   return ARCQ_OK;
 }
 
@@ -511,6 +812,10 @@ int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const flo
   if (!aligned(xhat, 16) || !aligned(packed_w, 16) || !aligned(y, 16))
     return fail(ARCQ_E_ALIGN, "xhat, packed_w and y must be 16-byte aligned");
   if (M == 0) return ARCQ_OK;
+  PairConfig pc;
+  if (choose_pair_config(M, N, K, bits, y_dtype == ARCQ_DT_F32, &pc))
+    return launch_pair_gemm(pc, xhat, packed_w, mu_w, sigma_w, codesum_w, w_codebook, bias, bits, M, N, K, y, y_dtype,
+                            stream);
   return launch_ws_gemm(false, xhat, packed_w, mu_w, sigma_w, codesum_w, w_codebook, bias, bits, M, N, K, y, y_dtype,
                         stream);
 }
@@ -544,15 +849,15 @@ int arcq_add_layernorm(const void* x, const void* y, const float* gamma, const f
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const __half *xh = static_cast<const __half*>(x), *yh = static_cast<const __half*>(y);
   __half *so = static_cast<__half*>(sum_out), *ho = static_cast<__half*>(h_out);
-  const bool plain = env_int("ARCQ_LN_PLAIN", 0) != 0;
+  const bool plain = opt(O_LN_PLAIN) != 0;
   if (K == 384 && !plain) {          // 16 lanes per row, 2 rows per warp
-    arcq::add_layernorm_rows_kernel<16><<<grid_for(M, 16, 6), 256, 0, st>>>(xh, yh, gamma, beta, eps, M, so, ho);
+    launch_pdl(arcq::add_layernorm_rows_kernel<16>, grid_for(M, 16, 6), 256, 0, st, xh, yh, gamma, beta, eps, M, so, ho);
   } else if (K == 192 && !plain) {
-    arcq::add_layernorm_rows_kernel<8><<<grid_for(M, 32, 6), 256, 0, st>>>(xh, yh, gamma, beta, eps, M, so, ho);
+    launch_pdl(arcq::add_layernorm_rows_kernel<8>, grid_for(M, 32, 6), 256, 0, st, xh, yh, gamma, beta, eps, M, so, ho);
   } else if (K == 768 && !plain) {
-    arcq::add_layernorm_rows_kernel<32><<<grid_for(M, 8, 6), 256, 0, st>>>(xh, yh, gamma, beta, eps, M, so, ho);
+    launch_pdl(arcq::add_layernorm_rows_kernel<32>, grid_for(M, 8, 6), 256, 0, st, xh, yh, gamma, beta, eps, M, so, ho);
   } else {
-    arcq::add_layernorm_kernel<<<grid_for(M, 8, 8), 256, 0, st>>>(xh, yh, gamma, beta, eps, M, static_cast<int>(K), so, ho);
+    launch_pdl(arcq::add_layernorm_kernel, grid_for(M, 8, 8), 256, 0, st, xh, yh, gamma, beta, eps, M, static_cast<int>(K), so, ho);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "add_layernorm launch");

@@ -106,7 +106,7 @@ __host__ __device__ inline WsSmem ws_smem_layout(int bn, int ws, int sa, int bit
   return s;
 }
 
-template <int BITS>
+template <int BITS, bool TRACE = false>
 __global__ void __launch_bounds__(kWsThreads, 1)
 packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                              const __grid_constant__ CUtensorMap tm_y, const WsParams p) {
@@ -157,6 +157,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   // Only the barriers and the tensor-memory allocation are set up before the roles part: the pair table and
   // the bias are filled by the roles that read them (builders, epilogue), so their global-memory latency does
   // not hold back the first TMA loads.
+  pdl_launch_dependents();
   if (tid == 0) {
     for (int i = 0; i < p.sa; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
     // a stationary slab never recycles a slot: its (up to 32) full barriers may run into the empty ones' space
@@ -179,9 +180,11 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
   tc_fence_after_sync();
   const uint32_t tmem_base = *s_tmem;
   bool ok = true;
-  long long* const tr = (p.trace != nullptr) ? p.trace + static_cast<long long>(blockIdx.x) * 128 : nullptr;
+  // Timestamps for the debugging entry point only: in the production instantiation (TRACE = false) `tr` is a
+  // compile-time null and every stamp below folds away.
+  long long* const tr = (TRACE && p.trace != nullptr) ? p.trace + static_cast<long long>(blockIdx.x) * 128 : nullptr;
   auto stamp = [&](int slot) {
-    if (tr != nullptr && slot < 128) {
+    if (TRACE && tr != nullptr && slot < 128) {
       long long t;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
       tr[slot] = t;
@@ -197,6 +200,9 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
     uint32_t w_slot = 0, w_ph = 1;                            // dense operand only
     const uint32_t sa = p.sa, wsn = p.ws;
     const int raw_x_step = raw_row_bytes(BITS);
+    // The activation (and, in the dense form, the weight matrix) may be the previous kernel's output.  The packed
+    // weight, its statistics and the bias are constants of the layer: the other roles read them without waiting.
+    pdl_wait();
     for (int b0 = 0; b0 < my_tiles; b0 += nbb) {
       const int nb = min(nbb, my_tiles - b0);
       for (int g = 0; g < G; ++g) {
@@ -283,7 +289,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
         for (int g = 0; g < G; ++g) ok = ok && mbar_wait_relaxed(&w_full[g], 0u, 32);
         w_waits = false;
       }
-      const bool st = tr != nullptr && batch == 2 && lane == 0;
+      const bool st = TRACE && tr != nullptr && batch == 2 && lane == 0;
       const uint32_t leader = lane == 0 ? 1u : 0u;
       if (!w_waits && nb == 1) {
         // steady state of a stationary slab: nothing but "A stage landed -> four MMAs -> free the stage"
@@ -351,6 +357,7 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
     asm volatile("bar.sync 2, 128;" ::: "memory");   // the four epilogue warps
     const int lq = warp & 3;  // tensor-memory lane quarter this warp may read
     uint32_t tile_seq = 0;
+    uint32_t half = 0;   // staging block of the next TMA store; alternates across tiles as well as within one
     for (int t = 0; t < my_tiles && ok; ++t, ++tile_seq) {
       const int tile = tile_of(t);
       const uint32_t buf = tile_seq & 1;
@@ -363,11 +370,11 @@ packed_weight_gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_a, const __g
       const uint32_t t_row = tmem_base + buf * 256 + (static_cast<uint32_t>(lq * 32) << 16);
       if (p.tma_store) {
         // 32 rows x 64 bytes per step (32 fp16 or 16 fp32 columns): registers -> staging block with the
-        // 64-byte swizzle (conflict-free 16-byte stores) -> one TMA store.  Two blocks per warp alternate,
-        // so a step only waits for the store issued two steps earlier to have read its block.
+        // 64-byte swizzle (conflict-free 16-byte stores) -> one TMA store.  Two blocks per warp alternate (from
+        // tile to tile too, so a tile with an odd number of steps does not reuse the block its last store
+        // is still reading), so a step only waits for the store issued two steps earlier to have read its block.
         uint8_t* const stg = sStage + lq * 4096;
         const int cw = p.y_f32 ? 16 : 32;
-        uint32_t half = 0;
         for (int c0 = 0; c0 < bn; c0 += cw, half ^= 1) {
           uint32_t acc[32];
           if (p.y_f32) {

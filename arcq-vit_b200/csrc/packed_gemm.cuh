@@ -90,6 +90,9 @@ __device__ __forceinline__ void rebuild_tile(uint8_t* tile, int rows_tile, long 
 
 template <int BITS>
 __global__ void __launch_bounds__(kGemmThreads, 1) packed_gemm_kernel(const GemmParams p) {
+  pdl_launch_dependents();   // the next kernel of the stream may start its set-up
+  pdl_wait();                // the input may be the previous kernel's output
+
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is what the 128-byte swizzle pattern is anchored to
   uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);

@@ -97,6 +97,14 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
   return false;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may become resident while the
+// kernel before it in the stream is still running.  pdl_wait() blocks until that kernel has completed and its
+// writes are visible (a no-op for an ordinary launch); pdl_launch_dependents() lets the kernel after this one
+// start early in the same way.  A kernel must not touch memory a predecessor writes before pdl_wait().
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -68,6 +68,28 @@ int arcq_device_status(void);
 int arcq_debug_trace(void* device_buffer);
 
 /*
+ * Debugging aid: tuning options of the launch code (slab widths, stage counts, kernel-variant switches,
+ * the poll limits of the kernels' bounded waits).  Each option has a built-in default; an environment
+ * variable of the same name, read once when the library is first used, overrides it, and so does this call
+ * at any time (process-wide).  Names: ARCQ_WS_BN, ARCQ_WS_SA, ARCQ_WS_WS, ARCQ_WS_STATIONARY, ARCQ_WS_NBB,
+ * ARCQ_WS_GRID, ARCQ_WS_TMA_STORE, ARCQ_WS_ROTATE, ARCQ_ACT_QUANT_V1, ARCQ_ACT_QUANT_V2, ARCQ_LN_PLAIN,
+ * ARCQ_PAIR, ARCQ_PAIR_MIN_M, ARCQ_PAIR_BN, ARCQ_PAIR_SA, ARCQ_PAIR_KS, ARCQ_PAIR_NBB, ARCQ_PAIR_LUT,
+ * ARCQ_PAIR_PAIRS, ARCQ_PAIR_STATIONARY, ARCQ_PAIR_WS, ARCQ_PAIR_FLAGS, ARCQ_PDL, ARCQ_POLL_LIMIT,
+ * ARCQ_SPIN_LIMIT.  Normal use sets none.
+ * Unknown names return ARCQ_E_BAD_ARG.  No reference counterpart.
+ */
+int arcq_debug_set_option(const char* name, int value);
+int arcq_debug_get_option(const char* name, int* value_out);
+
+/*
+ * Debugging aid: launches a one-warp kernel that waits, with the given poll limit (at most 65536), on a
+ * barrier nothing ever arrives on.  The wait runs out, the kernel leaves the code 0x7E57 in the device status
+ * word and returns: the path every bounded wait of the library takes instead of hanging.  Read the code with
+ * arcq_device_status().  No reference counterpart.
+ */
+int arcq_debug_wait_timeout(unsigned poll_limit, void* stream);
+
+/*
  * Activation quantizer: per row and per group of `group_size` consecutive
  * elements computes mean, scale = sqrt(mean(r^2)+1e-6), the code of every
  * element (number of thresholds below (x-mean)/scale) and the sum of code

@@ -408,19 +408,13 @@ def test_staged_quantizer_kernel_matches_oracle_and_the_parallel_kernel(pkg, ora
     assert np.array_equal(p.cpu().numpy(), oracle.pack(codes, bits))
     assert np.array_equal(m.cpu().numpy(), mu) and np.array_equal(s.cpu().numpy(), sg)
     assert np.array_equal(c.cpu().numpy(), cs)
-    os.environ["ARCQ_ACT_QUANT_V1"] = "1"                    # same input through the other kernel
-    try:
+    with pkg._cabi.option("ARCQ_ACT_QUANT_V1", 1):           # same input through the other kernel
         p1, m1, s1, c1 = pkg.ops.quantize_activation(xd, _t(th, cuda_device), _t(cb, cuda_device), bits, 64)
-    finally:
-        del os.environ["ARCQ_ACT_QUANT_V1"]
     assert torch.equal(p, p1) and torch.equal(m, m1) and torch.equal(s, s1) and torch.equal(c, c1)
     if dtype != torch.float32:                              # and through the two-lanes-per-group form
-        os.environ["ARCQ_ACT_QUANT_V2"] = "2"
-        try:
+        with pkg._cabi.option("ARCQ_ACT_QUANT_V2", 2):
             p2, m2, s2, c2 = pkg.ops.quantize_activation(xd, _t(th, cuda_device), _t(cb, cuda_device), bits, 64)
             xh2 = pkg.ops.quantize_activation_dequant(xd, _t(th, cuda_device), _t(cb, cuda_device), bits, 64, dtype)
-        finally:
-            del os.environ["ARCQ_ACT_QUANT_V2"]
         assert torch.equal(p, p2) and torch.equal(m, m2) and torch.equal(s, s2) and torch.equal(c, c2)
         assert torch.equal(xh2, pkg.ops.quantize_activation_dequant(xd, _t(th, cuda_device), _t(cb, cuda_device), bits, 64, dtype))
     # reconstruction output: one fused multiply-add per value here, three rounded steps in the reference;
@@ -484,11 +478,8 @@ def test_reconstruction_with_statistics_and_no_packed_output(pkg, oracle, cuda_d
     xh, m, s, c = _dequant_with_stats(pkg, xd, thd, cbd, bits)
     assert np.array_equal(m.cpu().numpy(), mu) and np.array_equal(s.cpu().numpy(), sg)
     assert np.array_equal(c.cpu().numpy(), cs)               # equal code sums <=> equal codes, group by group
-    os.environ["ARCQ_ACT_QUANT_V1"] = "1"                    # same call through the 8-lanes-per-group kernel
-    try:
+    with pkg._cabi.option("ARCQ_ACT_QUANT_V1", 1):           # same call through the 8-lanes-per-group kernel
         xh1, m1, s1, c1 = _dequant_with_stats(pkg, xd, thd, cbd, bits)
-    finally:
-        os.environ.pop("ARCQ_ACT_QUANT_V1", None)
     assert torch.equal(c, c1) and torch.equal(m, m1) and torch.equal(s, s1)
     if dtype == torch.float32:
         assert float((xh - xh1).abs().max()) <= 4e-6 * float(xh1.abs().max())
@@ -599,8 +590,7 @@ def test_two_lane_quantizer_search_and_zero_threshold_paths(pkg, oracle, cuda_de
     rng = np.random.default_rng(23)
     X = (rng.standard_normal((1023, 2560), dtype=np.float32) * 0.8).astype(np.float32)      # 40 920 groups
     X[7, :64] = 0.0
-    os.environ["ARCQ_ACT_QUANT_V2"] = "2"
-    try:
+    with pkg._cabi.option("ARCQ_ACT_QUANT_V2", 2):
         for dtype in (torch.float16, torch.bfloat16):
             x = torch.from_numpy(X).to(dtype)
             xr = x.float().numpy()
@@ -619,6 +609,4 @@ def test_two_lane_quantizer_search_and_zero_threshold_paths(pkg, oracle, cuda_de
                 codes, mu, sg, cs = oracle.quantize(xr, th, cb, 64)
                 p = pkg.ops.quantize_activation(x.to(cuda_device), _t(th, cuda_device), _t(cb, cuda_device), bits, 64)[0]
                 assert np.array_equal(p.cpu().numpy(), oracle.pack(codes, bits))
-    finally:
-        del os.environ["ARCQ_ACT_QUANT_V2"]
     assert pkg.ops.device_status() == 0
