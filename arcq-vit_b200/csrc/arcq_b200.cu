@@ -411,9 +411,9 @@ int max_resident_pairs(int bits, size_t smem) {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   cudaError_t e = cudaErrorUnknown;
-  if (bits == 4) e = cudaOccupancyMaxActiveClusters(&n, arcq::packed_weight_gemm_pair_kernel<4>, &cfg);
-  else if (bits == 3) e = cudaOccupancyMaxActiveClusters(&n, arcq::packed_weight_gemm_pair_kernel<3>, &cfg);
-  else e = cudaOccupancyMaxActiveClusters(&n, arcq::packed_weight_gemm_pair_kernel<2>, &cfg);
+  if (bits == 4) e = cudaOccupancyMaxActiveClusters(&n, arcq::packed_weight_gemm_pair_kernel<4, true>, &cfg);
+  else if (bits == 3) e = cudaOccupancyMaxActiveClusters(&n, arcq::packed_weight_gemm_pair_kernel<3, true>, &cfg);
+  else e = cudaOccupancyMaxActiveClusters(&n, arcq::packed_weight_gemm_pair_kernel<2, true>, &cfg);
   if (e != cudaSuccess || n <= 0) {
     cudaGetLastError();
     n = sm_count() / 2;
@@ -426,7 +426,10 @@ int max_resident_pairs(int bits, size_t smem) {
 
 template <int B>
 cudaError_t pair_set_smem(size_t smem) {
-  return cudaFuncSetAttribute(arcq::packed_weight_gemm_pair_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(arcq::packed_weight_gemm_pair_kernel<B, true>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(arcq::packed_weight_gemm_pair_kernel<B, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               static_cast<int>(smem));
 }
 
@@ -486,7 +489,7 @@ bool choose_pair_config(long long M, long long N, long long K, int bits, bool y_
       // issuing thread ahead of the tensor pipe
       k.ks = (G % 2 == 0) ? 2 : (G % 3 == 0) ? 3 : 1;
       if (opt(O_PAIR_KS) > 0 && G % opt(O_PAIR_KS) == 0) k.ks = opt(O_PAIR_KS);
-      k.ws = stationary ? G : (opt(O_PAIR_WS) > 0 ? opt(O_PAIR_WS) : 4);
+      k.ws = stationary ? G : (opt(O_PAIR_WS) > 0 ? opt(O_PAIR_WS) : (k.ks == 2 || k.ks == 3 ? 6 : 4));
       if (!stationary && k.ws > G) k.ws = G;
       if (k.ws > (stationary ? 32 : 16) || k.ws < k.ks || (!stationary && k.ws % k.ks != 0)) continue;
       // eight copies of the pair table (more did not measure faster); as many A stages as fit, eight sub-stages at most
@@ -784,9 +787,17 @@ static int launch_pair_gemm(const PairConfig& cfg, const void* xhat, const void*
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>(2 * cfg.pairs);
   // the dynamic shared-memory ceiling of the kernel was raised when the configuration was chosen
-  if (bits == 4) launch_pdl(arcq::packed_weight_gemm_pair_kernel<4>, grid, arcq::kPairThreads, cfg.smem, st, tm_a, tm_y, p);
-  else if (bits == 3) launch_pdl(arcq::packed_weight_gemm_pair_kernel<3>, grid, arcq::kPairThreads, cfg.smem, st, tm_a, tm_y, p);
-  else launch_pdl(arcq::packed_weight_gemm_pair_kernel<2>, grid, arcq::kPairThreads, cfg.smem, st, tm_a, tm_y, p);
+#define ARCQ_LAUNCH_PAIR(B)                                                                                              \
+  do {                                                                                                                  \
+    if (cfg.stationary)                                                                                                 \
+      launch_pdl(arcq::packed_weight_gemm_pair_kernel<B, true>, grid, arcq::kPairThreads, cfg.smem, st, tm_a, tm_y, p);  \
+    else                                                                                                                \
+      launch_pdl(arcq::packed_weight_gemm_pair_kernel<B, false>, grid, arcq::kPairThreads, cfg.smem, st, tm_a, tm_y, p); \
+  } while (0)
+  if (bits == 4) ARCQ_LAUNCH_PAIR(4);
+  else if (bits == 3) ARCQ_LAUNCH_PAIR(3);
+  else ARCQ_LAUNCH_PAIR(2);
+#undef ARCQ_LAUNCH_PAIR
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "packed_weight_gemm (pair) launch");
   return ARCQ_OK;

@@ -427,13 +427,13 @@ __device__ __forceinline__ bool pair_build_jobs(const PairBuildCtx& c, int bt, i
   return ok;
 }
 
-template <int BITS>
+template <int BITS, bool STATIONARY>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 packed_weight_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_y,
                                const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  const PairSmem L = pair_smem_layout(p.bn, p.ws, p.sa, p.ks, p.G, p.stationary != 0, p.lut_shift);
+  const PairSmem L = pair_smem_layout(p.bn, p.ws, p.sa, p.ks, p.G, STATIONARY, p.lut_shift);
   uint8_t* const sA = smem + L.a;
   uint8_t* const sW = smem + L.w;
   uint8_t* const sStage = smem + L.stage;
@@ -472,7 +472,7 @@ packed_weight_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const _
     return (rank + q * pairs_in_slab) * kPairTileM + static_cast<int>(crank) * kTileM;
   };
   const int nbb = p.nbb;
-  const bool stationary = p.stationary != 0;
+  constexpr bool stationary = STATIONARY;
   const uint32_t poll_limit = p.poll_limit, spin_limit = p.spin_limit;
   const uint32_t stage_bytes = static_cast<uint32_t>(ks) * kStageA;
   const uint32_t wtile_bytes = static_cast<uint32_t>(hb) * 128u;
@@ -724,11 +724,11 @@ packed_weight_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const _
       c.stationary = stationary;
       c.tr = tr;
       c.tr_base = is_epi ? 224 : 200;
-      // A stationary slab is built once, while the epilogue warps have nothing to drain yet: the two groups
-      // alternate on its sub-tiles (each sub-tile is still the work of eight warps).  A streaming ring is
-      // rebuilt for every batch of tiles by the weight warps alone.
-      const int first = stationary ? (is_epi ? 1 : 0) : 0, stride = stationary ? 2 : 1;
-      if (stationary || !is_epi) ok = pair_build_jobs<BITS>(c, bt, lane, first, stride, fills * G, true);
+      // A slab that is walked once (stationary, or a streaming ring with a single batch of tiles) is built while
+      // the epilogue warps have nothing to drain yet: the two groups alternate on its sub-tiles (each sub-tile is
+      // still the work of eight warps).  A ring that is walked several times is rebuilt by the weight warps alone.
+      if (stationary || fills == 1) ok = pair_build_jobs<BITS>(c, bt, lane, is_epi ? 1 : 0, 2, fills * G, true);
+      else if (!is_epi) ok = pair_build_jobs<BITS>(c, bt, lane, 0, 1, fills * G, true);
       else asm volatile("bar.sync 1, %0;" ::"r"(n_builders) : "memory");   // only orders the table fill above
       if (tid == 2 * 32) stamp(8);
       if (tid == (2 + kPairEpiWarps) * 32) stamp(9);
