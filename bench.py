@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="eager launches instead of CUDA-graph replay")
     ap.add_argument("--cpu-sample", type=int, default=8, help="images in the CPU-baseline sample batch")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-side-records", action="store_true",
+                    help="leave out the batch-1 record, the memory columns and the reference Triton baseline")
     ap.add_argument("--kernels-only", action="store_true",
                     help="time only the two kernels of the packed linear on the model's layer shapes (for profiling)")
     ap.add_argument("--layers", default="qkv,proj,fc1,fc2", help="layer shapes for --kernels-only")
@@ -109,42 +111,70 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------- CPU path
+def _ref_runner():
+    """baseline/ref_runner.py when the reference's files are installed under baseline/_ref, else None."""
+    sys.path.insert(0, str(ROOT / "baseline"))
+    try:
+        import ref_runner
+        return ref_runner if ref_runner.available() else None
+    except Exception:
+        return None
+    finally:
+        sys.path.pop(0)
+
+
 def cpu_reference_run(a, steps: int, warmup: int, sample_images: int):
-    """The reference's CPU fake-quant forward, as restated by the oracle, on all host cores."""
-    from oracle.fakequant_vit import OracleViT
-    O = entry.import_oracle()
+    """The reference's CPU fake-quant forward on all host cores: its own ``QuantLinearPCARCQ`` layers
+    (quant_backends.py:282-322) when ``baseline/_ref`` is installed (kind "reference"), else the oracle's
+    restatement of them (kind "port")."""
+    import contextlib
     pkg = entry.import_package()
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    O.set_threads(cores)
-    m = pkg.create_vit(a.model, seed=0)
-    dim, heads, depth = pkg.DEIT_CONFIGS[a.model]
-    o = OracleViT(m.state_dict(), dim, heads, depth, a.bits, cache_weights=False)
     imgs = torch.randn(sample_images, 3, 224, 224, generator=torch.Generator().manual_seed(1))
-    o(imgs)                                   # calibrating forward (codebook compile), not timed
-    for _ in range(max(0, warmup - 1)):
-        o(imgs)
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        o(imgs)
-    dt = time.perf_counter() - t0
-    return dict(value=sample_images * steps / dt, ms_per_step=1e3 * dt / steps, cores=cores,
-                sample=f"{steps} forwards of a {sample_images}-image batch of the same model after {warmup} warm-up")
+    rr = _ref_runner()
+    if rr is not None:
+        kind = "reference"
+        with contextlib.redirect_stdout(sys.stderr):          # the reference logs every codebook compile to stdout
+            model = rr.reference_cpu_model(pkg, a.model, a.bits, imgs)   # includes the calibrating forward
+        run = lambda: model(imgs)                                             # noqa: E731
+    else:
+        kind = "port"
+        from oracle.fakequant_vit import OracleViT
+        O = entry.import_oracle()
+        O.set_threads(cores)
+        m = pkg.create_vit(a.model, seed=0)
+        dim, heads, depth = pkg.DEIT_CONFIGS[a.model]
+        o = OracleViT(m.state_dict(), dim, heads, depth, a.bits, cache_weights=False)
+        o(imgs)                                   # calibrating forward (codebook compile), not timed
+        run = lambda: o(imgs)                                                 # noqa: E731
+    with torch.no_grad():
+        for _ in range(max(0, warmup - 1)):
+            run()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            run()
+        dt = time.perf_counter() - t0
+    return dict(value=sample_images * steps / dt, ms_per_step=1e3 * dt / steps, cores=cores, kind=kind,
+                sample=f"{steps} forwards of a {sample_images}-image batch of the same model after one calibrating "
+                       f"forward and {max(0, warmup - 1)} warm-up")
 
 
 def run_reference_arm(a):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = min(a.steps, 3), max(1, min(a.warmup, 2))
+    steps, warmup = min(a.steps, 2), max(1, min(a.warmup, 2))
     r = cpu_reference_run(a, steps, warmup, a.cpu_sample)
+    what = ("the reference's own QuantLinearPCARCQ layers (baseline/_ref)" if r["kind"] == "reference"
+            else "oracle port of the reference's fake-quant layers")
     line = {
         "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "images/s", "n_gpus": a.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(a), "note": "CPU fake-quant path of the reference (oracle port), "
+        "config": {"workload": workload_name(a), "note": f"CPU fake-quant path: {what}, "
                    f"{a.cpu_sample}-image batches on host cores"},
-        "cpu_baseline": {"value": r["value"], "unit": "images/s", "cores": r["cores"], "kind": "port",
+        "cpu_baseline": {"value": r["value"], "unit": "images/s", "cores": r["cores"], "kind": r["kind"],
                          "sample": r["sample"]},
         "e2e": {"value": r["value"], "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -243,6 +273,83 @@ def kernel_rooflines(pkg, a, dev, pk):
     return out
 
 
+def _time_forward(runner, x, warm: int, iters: int) -> float:
+    """Milliseconds per call of ``runner(x)`` (CUDA events on the current stream)."""
+    with torch.no_grad():
+        for _ in range(warm):
+            runner(x)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            runner(x)
+        e1.record()
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def _memory_columns(model) -> dict:
+    """The memory columns of the reference's benchmark protocol (scripts/benchmark_arcq_on_the_fly.py:247-261)."""
+    mb = 1024 * 1024
+    params = sum(p.numel() * p.element_size() for p in model.parameters()) / mb
+    bufs = sum(b.numel() * b.element_size() for b in model.buffers()) / mb
+    return dict(param_mb=params, buffer_mb=bufs, persistent_mb=params + bufs)
+
+
+def small_batch_record(pkg, a, dev, model, batch: int = 1):
+    """Batch-1 forward (weight-bandwidth- and launch-bound): latency, images/s and the packed-weight bytes per
+    second it streams; the reference's protocol at bs = 1 (CUDA-graph replay, 10 warm-up / 50 timed)."""
+    x = torch.randn(batch, 3, 224, 224, generator=torch.Generator().manual_seed(5)).half().to(dev)
+    torch.cuda.reset_peak_memory_stats()
+    resident = torch.cuda.memory_allocated() / 1024 / 1024
+    g = pkg.GraphedModel(model, x)
+    ms = _time_forward(g, x, 10, 50)
+    peak = torch.cuda.max_memory_allocated() / 1024 / 1024
+    packed_bytes = sum(b.numel() * b.element_size() for n, b in model.named_buffers()
+                       if any(k in n for k in ("packed_weight_codes", "weight_center", "weight_scale", "weight_code_sum",
+                                               "bias_tensor")))
+    rec = dict(batch=batch, ms=ms, images_per_s=batch * 1e3 / ms, packed_weight_mb=packed_bytes / 1e6,
+               packed_weight_gbs=packed_bytes / ms / 1e6, resident_model_mb=resident, forward_peak_mb=peak,
+               forward_delta_mb=peak - resident)
+    del g
+    return rec
+
+
+def triton_baseline_run(pkg, a, dev, batches):
+    """The reference's Triton on-the-fly path (its own ARCQPackedLinearOnTheFly, unmodified, from baseline/_ref)
+    on the same packed buffers and the same inputs, CUDA-graph replay like the B200 arm, timed in this run."""
+    rr = _ref_runner()
+    if rr is None:
+        return {"unavailable": "baseline/_ref is not installed (python baseline/install_ref.py --reference <checkout>)"}
+    out = {"kind": "reference Triton path (fair_qat/arcq_packed_on_the_fly.py + arcq_packed_triton.py), CUDA graph",
+           "protocol": "10 warm-up / 50 timed replays, CUDA events"}
+    try:
+        import contextlib
+        gen = torch.Generator().manual_seed(100)
+        calib = torch.randn(a.batch, 3, 224, 224, generator=gen).half().to(dev)
+        model = pkg.create_vit(a.model, seed=0).half().to(dev)
+        with torch.no_grad(), contextlib.redirect_stdout(sys.stderr):
+            model = pkg.quantise_model(model, calib, a.bits)
+            ref_model = rr.reference_triton_model(pkg, model)
+        for b in batches:
+            x = calib if b == a.batch else torch.randn(b, 3, 224, 224, generator=gen).half().to(dev)
+            with contextlib.redirect_stdout(sys.stderr):
+                try:
+                    runner = pkg.GraphedModel(ref_model, x, warmup=5)
+                    how = "graph"
+                except Exception:                     # fall back to eager launches if capture is refused
+                    torch.cuda.synchronize()
+                    runner, how = ref_model, "eager"
+                ms = _time_forward(runner, x, 10, 50)
+            out[f"bs{b}"] = dict(ms=ms, images_per_s=b * 1e3 / ms, launch=how)
+        out.update(_memory_columns(ref_model))
+        del ref_model, model
+        torch.cuda.empty_cache()
+    except Exception as ex:                           # Triton missing, compile failure, ...
+        return {"unavailable": f"unavailable on this box: {type(ex).__name__}: {str(ex)[:300]}"}
+    return out
+
+
 def run_gpu_arm(a):
     pkg = entry.import_package()
     pkg._cabi.load()                      # raises if the CUDA library is not built: there is no fallback
@@ -323,10 +430,18 @@ def run_gpu_arm(a):
     if rank == 0:
         pk = peaks()
         extra = kernel_rooflines(pkg, a, dev, pk)
+        if world == 1 and not a.skip_side_records:
+            extra["bs1"] = small_batch_record(pkg, a, dev, model, 1)
+            extra["memory"] = _memory_columns(model)
+            tb = triton_baseline_run(pkg, a, dev, sorted({a.batch, 1}, reverse=True))
+            if f"bs{a.batch}" in tb:
+                tb["b200_over_triton"] = {f"bs{a.batch}": tb[f"bs{a.batch}"]["ms"] / (ms / a.steps),
+                                          "bs1": tb["bs1"]["ms"] / extra["bs1"]["ms"] if "bs1" in tb else None}
+            extra["triton_baseline"] = tb
         cpu = None
         if world == 1 and not a.skip_cpu_baseline:
-            r = cpu_reference_run(a, 2, 1, a.cpu_sample)
-            cpu = {"value": r["value"], "unit": "images/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]}
+            r = cpu_reference_run(a, 1, 1, a.cpu_sample)
+            cpu = {"value": r["value"], "unit": "images/s", "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]}
         act_bytes = B * TOKENS * pkg.DEIT_CONFIGS[a.model][0] * 2
         line = {
             "metric": METRIC, "value": global_batch * a.steps / (ms / 1e3), "unit": "images/s", "n_gpus": world,
