@@ -356,7 +356,7 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
       // tensor ops, written back over this thread's staged row and copied out coalesced by the block
       static_assert(!WRITE_XHAT || sizeof(XH) <= sizeof(T), "reconstruction must fit the staged row");
       static_assert(kAq2Threads * 4 == 512, "the code extraction above assumes a 512-byte table step");
-      const float mean_f = fmaf(-scale, code_sum * (1.0f / 64.0f), mean);
+      const float vm = __fmul_rn(code_sum, 1.0f / 64.0f);   // exact: a power of two
       constexpr int kOutChunks = 64 * sizeof(XH) / 16;   // 16-byte chunks of one output row
       constexpr int kPer = 16 / sizeof(XH);               // values per chunk
 #pragma unroll
@@ -365,10 +365,10 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int e = kPer * c + (kPer / 4) * j;
-          // mean + scale*(cb - vm) evaluated as one fused multiply-add around mean - scale*vm: equal to the
-          // reference's three rounded steps to within an ulp of fp32, far below the rounding of the output type
-          const float f0 = fmaf(scale, v[e], mean_f);
-          const float f1 = (kPer == 8) ? fmaf(scale, v[e + (kPer == 8 ? 1 : 0)], mean_f) : 0.0f;
+          // mean + scale*(cb - vm) in the reference's three rounded steps, so that the result is the same
+          // bits whichever quantizer kernel (and therefore whichever batch size) produced it
+          const float f0 = __fadd_rn(mean, __fmul_rn(scale, __fsub_rn(v[e], vm)));
+          const float f1 = (kPer == 8) ? __fadd_rn(mean, __fmul_rn(scale, __fsub_rn(v[e + (kPer == 8 ? 1 : 0)], vm))) : 0.0f;
           o[j] = aq2_pack2<XH>(f0, f1);
         }
         *reinterpret_cast<uint4*>(row + 16 * c) = make_uint4(o[0], o[1], o[2], o[3]);

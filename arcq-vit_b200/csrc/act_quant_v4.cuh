@@ -285,11 +285,12 @@ __global__ void __launch_bounds__(kAq4Threads, 4) act_quant_v4_kernel(const T* _
       // mean + scale*(cb - code_sum/64) as one fused multiply-add around mean - scale*code_sum/64 (the same
       // expression as the one-thread-per-group kernel), written over this lane's staged values and copied
       // out coalesced by the block
-      const float mean_f = fmaf(-scale, code_sum * (1.0f / 64.0f), mean);
+      const float vm = __fmul_rn(code_sum, 1.0f / 64.0f);   // exact: a power of two
+      auto rec = [&](float cbv) { return __fadd_rn(mean, __fmul_rn(scale, __fsub_rn(cbv, vm))); };   // the reference's three rounded steps
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        const uint32_t lo = aq2_pack2<T>(fmaf(scale, v[4 * c], mean_f), fmaf(scale, v[4 * c + 1], mean_f));
-        const uint32_t hi = aq2_pack2<T>(fmaf(scale, v[4 * c + 2], mean_f), fmaf(scale, v[4 * c + 3], mean_f));
+        const uint32_t lo = aq2_pack2<T>(rec(v[4 * c]), rec(v[4 * c + 1]));
+        const uint32_t hi = aq2_pack2<T>(rec(v[4 * c + 2]), rec(v[4 * c + 3]));
         *reinterpret_cast<uint2*>(row + 16 * c) = make_uint2(lo, hi);
       }
       __syncthreads();

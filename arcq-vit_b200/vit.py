@@ -141,7 +141,7 @@ def create_vit(name: str, seed: int = 0, num_classes: int = 1000) -> VisionTrans
 
 
 def quantised_linear_names(model: nn.Module) -> List[str]:
-    """Paths of the linears BASELINE quantises: qkv / proj / fc1 / fc2 of every block, forward order."""
+    """Paths of the quantised linears: qkv / proj / fc1 / fc2 of every block, forward order."""
     out = []
     for i, _ in enumerate(model.blocks):
         out += [f"blocks.{i}.attn.qkv", f"blocks.{i}.attn.proj", f"blocks.{i}.mlp.fc1", f"blocks.{i}.mlp.fc2"]

@@ -25,12 +25,16 @@ from . import arcq_oracle as O
 
 class OracleViT:
     def __init__(self, state_dict: Dict[str, torch.Tensor], dim: int, heads: int, depth: int, bits: int,
-                 group_size: int = 64, patch: int = 16, cache_weights: bool = True):
+                 group_size: int = 64, patch: int = 16, cache_weights: bool = True, fp16_operands: bool = False):
         self.sd = {k: v.detach().float().cpu() for k, v in state_dict.items()}
         self.dim, self.heads, self.depth, self.bits, self.gs, self.patch = dim, heads, depth, bits, group_size, patch
         # the reference fake-quantises the weight again on every forward (quant_backends.py:320);
         # cache_weights=False does the same (for timing), True keeps the identical result (for tests)
         self.cache_weights = cache_weights
+        # True: both fake-quantised operands are rounded to fp16 before the fp32 contraction (what any half-precision
+        # tensor-core path does to them); everything else unchanged.  Used to measure how far a rounding-only change
+        # moves the logits of this model.
+        self.fp16_operands = fp16_operands
         self.codebooks: Dict[str, Dict[str, np.ndarray]] = {}
         self._w_hat: Dict[str, np.ndarray] = {}
 
@@ -56,7 +60,10 @@ class OracleViT:
         ca, mu, sg, _ = O.quantize(x2, c["act_th"], c["act_cb"], self.gs)
         xf = np.ascontiguousarray(x2, np.float32)
         x_hat = xf + (O.dequant(ca, mu, sg, c["act_cb"], self.gs) - xf)
-        y = torch.from_numpy(x_hat) @ torch.from_numpy(self._w_hat[name]).T
+        xt, wt = torch.from_numpy(x_hat), torch.from_numpy(self._w_hat[name])
+        if self.fp16_operands:
+            xt, wt = xt.half().float(), wt.half().float()
+        y = xt @ wt.T
         if b is not None:
             y = y + torch.from_numpy(b)
         if capture is not None:

@@ -1,3 +1,5 @@
+import json
+import os
 import sys
 from pathlib import Path
 
@@ -68,3 +70,17 @@ def cuda_device():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(scope="session")
+def report(tmp_path_factory):
+    """Append one JSON record per call to ``parity_report.jsonl`` in the directory named by the environment
+    variable ARCQ_REPORT_DIR, or in pytest's temporary directory when it is unset."""
+    d = os.environ.get("ARCQ_REPORT_DIR")
+    out = Path(d) if d else tmp_path_factory.getbasetemp()
+    out.mkdir(parents=True, exist_ok=True)
+
+    def write(name, **kw):
+        with open(out / "parity_report.jsonl", "a") as f:
+            f.write(json.dumps(dict(test=name, **kw)) + "\n")
+    return write

@@ -34,7 +34,7 @@ HERE = Path(__file__).resolve().parent
 
 # name -> (M, K, N, bits, seed, outliers)
 CASES = {
-    # BASELINE config 1: X [8*197, 384] ~ N(0,1) with 4 channels x20, W [1536,384] ~ N(0,0.02)
+    # the single-linear configuration: X [8*197, 384] ~ N(0,1) with 4 channels x20, W [1536,384] ~ N(0,0.02)
     "c1_w4a4": dict(M=8 * 197, K=384, N=1536, bits=4, seed=0, outliers=4),
     "c1_w3a3": dict(M=8 * 197, K=384, N=1536, bits=3, seed=0, outliers=4),
     # ragged / small cases: one group, odd row count; 3-bit rows of 72 bytes (K=192)

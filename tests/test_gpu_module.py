@@ -13,14 +13,10 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-2
 
 
-def _report(name, **kw):
-    (ROOT / "gpurun_out").mkdir(exist_ok=True)
-    with open(ROOT / "gpurun_out" / "parity_report.jsonl", "a") as f:
-        f.write(json.dumps(dict(test=name, **kw)) + "\n")
 
 
 @pytest.mark.parametrize("name", ["c1_w4a4", "c1_w3a3", "edge_k192_w3a3"])
-def test_packed_linear_forward_is_a_drop_in(pkg, oracle, golden, cuda_device, name):
+def test_packed_linear_forward_is_a_drop_in(pkg, oracle, golden, cuda_device, name, report):
     g = golden(name)
     y_ref, _ = oracle.fake_quant_linear(g["X"], g["W"], g["b"], g["act_thresholds"], g["act_codebook"],
                                         g["w_thresholds"], g["w_codebook"], g["gs"])
@@ -39,7 +35,7 @@ def test_packed_linear_forward_is_a_drop_in(pkg, oracle, golden, cuda_device, na
     y16 = otf(xh)
     assert y16.dtype == torch.float16
     err16 = float(np.abs(y16.float().cpu().numpy() - y_ref16).max() / rms)
-    _report("packed_linear_module", case=name, fp32_chain=err, half_chain=err16)
+    report("packed_linear_module", case=name, fp32_chain=err, half_chain=err16)
     assert err16 < TOL
     with pytest.raises(ValueError):
         layer(torch.zeros(2, g["K"] + 64, device=cuda_device))
@@ -60,7 +56,7 @@ def _models(pkg, name, bits, batch, dev, depth=None):
 
 
 @pytest.mark.parametrize("name,bits", [("deit_tiny", 4), ("deit_small", 3)])
-def test_whole_model_teacher_forced_parity(pkg, oracle, cuda_device, name, bits):
+def test_whole_model_teacher_forced_parity(pkg, oracle, cuda_device, name, bits, report):
     """Every quantised linear of the model, fed the oracle's own input to that layer: activation codes
     bit-exact, outputs within 2e-2 of the output RMS -- on real whole-model activation statistics."""
     o, packed, imgs = _models(pkg, name, bits, 4, cuda_device)
@@ -82,11 +78,11 @@ def test_whole_model_teacher_forced_parity(pkg, oracle, cuda_device, name, bits)
         err = float(np.abs(y - ref).max() / np.sqrt((ref.astype(np.float64) ** 2).mean()))
         worst = max(worst, err)
         assert err < TOL, f"{lname}: max|dy|/rms = {err:.3e}"
-    _report("teacher_forced", model=name, bits=bits, layers=len(o.layer_names()), worst_max_abs_over_rms=worst)
+    report("teacher_forced", model=name, bits=bits, layers=len(o.layer_names()), worst_max_abs_over_rms=worst)
     assert pkg.ops.device_status() == 0
 
 
-def test_whole_model_free_running_agreement_is_reported(pkg, oracle, cuda_device):
+def test_whole_model_free_running_agreement_is_reported(pkg, oracle, cuda_device, report):
     """Free-running fp16 chain against the fp32 CPU oracle.  On random-init models with noise images the
     top-1 margin is tiny and a single flipped code changes later layers, so agreement is reported (with
     the logit error) rather than asserted at the 99.5 % bar; the layer-wise test above is the gate."""
@@ -97,7 +93,7 @@ def test_whole_model_free_running_agreement_is_reported(pkg, oracle, cuda_device
     assert torch.isfinite(got).all() and got.shape == (16, 1000)
     agree = float((got.argmax(-1) == ref.argmax(-1)).float().mean())
     top2 = ref.topk(2, dim=-1).values
-    _report("free_running", model="deit_tiny", bits=4, images=16, top1_agreement=agree,
+    report("free_running", model="deit_tiny", bits=4, images=16, top1_agreement=agree,
             max_abs_logit_diff=float((got - ref).abs().max()), ref_logit_std=float(ref.std()),
             ref_median_top1_margin=float((top2[:, 0] - top2[:, 1]).median()))
     assert float((got - ref).abs().max()) < 0.5 * float(ref.std()) + 0.5
