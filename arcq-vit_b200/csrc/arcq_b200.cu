@@ -985,6 +985,19 @@ int arcq_packed_linear_static_scratch(const void* xhat, const uint8_t* packed_w,
     return fail(ARCQ_E_TOO_LARGE, "weight of %lld x %lld values exceeds the static scratch of %lld values; "
                                   "use arcq_dequant + arcq_dense_weight_gemm with a buffer of your own",
                 (long long)N, (long long)K, (long long)kStaticWeightElems);
+  // everything the two launches below would reject is rejected here, before the first of them runs and
+  // overwrites the shared scratch
+  if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
+  if (y_dtype != ARCQ_DT_F16 && y_dtype != ARCQ_DT_F32) return fail(ARCQ_E_BAD_ARG, "y_dtype must be f16 or f32");
+  if (K % 64 != 0) return fail(ARCQ_E_UNSUPPORTED, "K=%lld: this entry point needs K %% 64 == 0", (long long)K);
+  if (N % 16 != 0) return fail(ARCQ_E_UNSUPPORTED, "N=%lld: this entry point needs N %% 16 == 0", (long long)N);
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > (1 << 20)) return fail(ARCQ_E_TOO_LARGE, "shape too large");
+  if (!aligned(xhat, 16) || !aligned(y, 16)) return fail(ARCQ_E_ALIGN, "xhat and y must be 16-byte aligned");
+  if (!aligned(packed_w, 4)) return fail(ARCQ_E_ALIGN, "packed codes must be 4-byte aligned");
+  if (M > 0) {
+    WsConfig probe;
+    if (!choose_ws_config(M, N, K, 4, true, &probe)) return fail(ARCQ_E_UNSUPPORTED, "no tile configuration for this shape");
+  }
   __half* const w16 = static_weight_scratch();
   if (w16 == nullptr) return ARCQ_E_CUDA;
   if (M == 0) return ARCQ_OK;

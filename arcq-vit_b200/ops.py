@@ -183,9 +183,14 @@ def add_layernorm(x: torch.Tensor, y, norm: torch.nn.LayerNorm):
     K = shape[-1]
     x2 = _dev(x.reshape(-1, K), "x", torch.float16)
     y2 = None if y is None else _dev(y.reshape(-1, K), "y", torch.float16)
-    if not hasattr(norm, "_arcq_f32"):          # fp32 copies of the affine parameters, made once
-        norm._arcq_f32 = (norm.weight.detach().float().contiguous(), norm.bias.detach().float().contiguous())
-    g32, b32 = norm._arcq_f32
+    # fp32 copies of the affine parameters, remade whenever the parameters were replaced, written to or moved
+    key = (norm.weight.data_ptr(), norm.weight._version, norm.bias.data_ptr(), norm.bias._version, x2.device)
+    cached = getattr(norm, "_arcq_f32", None)
+    if cached is None or cached[0] != key:
+        cached = (key, norm.weight.detach().to(device=x2.device, dtype=torch.float32).contiguous(),
+                  norm.bias.detach().to(device=x2.device, dtype=torch.float32).contiguous())
+        norm._arcq_f32 = cached
+    _, g32, b32 = cached
     h = torch.empty_like(x2)
     s_out = torch.empty_like(x2) if y2 is not None else None
     if x2.shape[0] > 0:

@@ -110,3 +110,4 @@ def test_a_wait_that_runs_out_sets_the_status_word_and_returns(pkg, cuda_device)
     y = _run(pkg, a, 4, torch.float16)
     ref = _fp64(pkg, a, 4)
     assert float((y.double() - ref).abs().max() / ref.pow(2).mean().sqrt()) < 6e-3
+

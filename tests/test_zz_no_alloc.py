@@ -94,3 +94,28 @@ def test_static_scratch_linear_rejects_a_weight_beyond_its_capacity(pkg, cuda_de
     # a null pointer is refused before anything else
     assert lib.arcq_packed_linear_static_scratch(None, pw.data_ptr(), st.data_ptr(), st.data_ptr(), st.data_ptr(),
                                                  dummy.data_ptr(), None, 4, 64, 8, N, K, y.data_ptr(), 1, None) == -1
+
+
+def test_static_scratch_linear_rejects_bad_arguments_before_its_first_launch(pkg, cuda_device):
+    """What either of its two launches would refuse (output type, N not a multiple of 16, a misaligned output) is
+    refused up front, so a rejected call never gets as far as overwriting the shared weight scratch."""
+    lib = pkg._cabi.load()
+    M, K, N = 64, 384, 384
+    dummy = torch.zeros(16, dtype=torch.float32, device=cuda_device)
+    x = torch.zeros(M, K, dtype=torch.float16, device=cuda_device)
+    pw = torch.zeros(N, K // 2, dtype=torch.uint8, device=cuda_device)
+    st = torch.zeros(N, K // 64, dtype=torch.float32, device=cuda_device)
+    y = torch.zeros(M * N + 8, dtype=torch.float16, device=cuda_device)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call(n=N, k=K, ydt=1, yptr=None, bits=4):
+        return lib.arcq_packed_linear_static_scratch(x.data_ptr(), pw.data_ptr(), st.data_ptr(), st.data_ptr(), st.data_ptr(),
+                                                     dummy.data_ptr(), None, bits, 64, M, n, k,
+                                                     y.data_ptr() if yptr is None else yptr, ydt, stream)
+    assert call(ydt=2) == -1 and b"y_dtype" in lib.arcq_last_error_string()          # bf16 output is not built
+    assert call(n=N - 8) == -3                                                        # N % 16 != 0
+    assert call(yptr=y.data_ptr() + 2) == -4                                          # misaligned output
+    assert call(bits=5) == -1
+    assert call() == 0                                                                # and the plain call still runs
+    torch.cuda.synchronize()
+    assert pkg.ops.device_status() == 0
