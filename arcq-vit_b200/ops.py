@@ -276,3 +276,70 @@ def dequant(packed, center, scale, code_sum, codebook, bits: int, group_size: in
                             codebook.data_ptr(), bits, group_size, R, K, out.data_ptr(), _DT[out_dtype], _stream()),
            "arcq_dequant")
     return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# The reference extension's exact operator signatures (arcq_infer_bind.cpp:57-66), for a shim that replaces
+# `fair_qat/arcq_infer_cuda/__init__.py` without touching the reference's module classes.
+_PRODUCT_TABLE_CACHE: dict = {}
+
+
+def codebooks_from_product_table(product_table: torch.Tensor, packed_x: torch.Tensor, x_code_sum: torch.Tensor,
+                                 bits: int, group_size: int):
+    """(act_codebook, w_codebook) from ``product_table = outer(act_codebook, w_codebook)``.
+
+    The reference operator is given only the table (arcq_packed_linear.py:114-117 builds it, :199-213 passes it);
+    the kernels here rebuild each operand from its own codebook.  A rank-one table fixes the two factors up to one
+    scale, and the activation code sums fix that scale: the sum of the (scaled) activation codebook over the codes
+    of a group equals scale x that group's ``x_code_sum``.  Everything runs on the device without a
+    synchronisation; the result is cached per table (the module's buffer), so a layer pays for it once.
+    """
+    key = (product_table.data_ptr(), product_table._version, str(product_table.device))
+    hit = _PRODUCT_TABLE_CACHE.get(key)
+    if hit is not None:
+        return hit
+    T = product_table.float()
+    j0 = T.abs().amax(0).argmax().view(1)
+    a1 = T.index_select(1, j0).squeeze(1)                                   # act_codebook * w_codebook[j0]
+    i0 = a1.abs().argmax().view(1)
+    w1 = T.index_select(0, i0).squeeze(0) / a1.index_select(0, i0)         # w_codebook / w_codebook[j0]
+    G = x_code_sum.shape[1]
+    flat = x_code_sum.abs().reshape(-1).argmax().view(1)                    # the group with the largest code sum
+    row, grp = flat // G, flat % G
+    codes = unpack_codes_u8(packed_x.index_select(0, row).contiguous(), bits, G * group_size)
+    codes_g = codes.view(G, group_size).index_select(0, grp).long().view(-1)
+    c = a1[codes_g].sum() / x_code_sum.reshape(-1).index_select(0, flat).squeeze(0)     # = w_codebook[j0]
+    out = ((a1 / c).contiguous(), (w1 * c).contiguous())
+    if len(_PRODUCT_TABLE_CACHE) > 4096:
+        _PRODUCT_TABLE_CACHE.clear()
+    _PRODUCT_TABLE_CACHE[key] = out
+    return out
+
+
+def arcq_linear_forward_product_table(packed_x, x_center, x_scale, x_code_sum, packed_w, w_center, w_scale, w_code_sum,
+                                      product_table, bias, bits: int, group_size: int, in_features: int,
+                                      out_features: int) -> torch.Tensor:
+    """``arcq_linear_forward`` with the reference's argument list (product table instead of two codebooks)."""
+    act_cb, w_cb = codebooks_from_product_table(product_table, packed_x, x_code_sum, bits, group_size)
+    return arcq_linear_forward(packed_x, x_center, x_scale, x_code_sum, packed_w, w_center, w_scale, w_code_sum,
+                               act_cb, w_cb, bias, bits, group_size, in_features, out_features)
+
+
+def quantize_activation_u8(x: torch.Tensor, thresholds: torch.Tensor, codebook: torch.Tensor, bits: int, group_size: int):
+    """[codes uint8 [M,K] (one byte per code), center, scale, code_sum]: the reference's ``quantize_activation_u8``
+    (arcq_activation_kernel.cu:239-284).  Same quantizer kernel, codes unpacked afterwards."""
+    packed, mu, sg, cs = quantize_activation(x, thresholds, codebook, bits, group_size)
+    return unpack_codes_u8(packed, bits, x.shape[1]), mu, sg, cs
+
+
+def arcq_linear_forward_u8(x_codes, x_center, x_scale, x_code_sum, w_codes, w_center, w_scale, w_code_sum,
+                           product_table, bias, group_size: int) -> torch.Tensor:
+    """The reference's ``arcq_linear_forward_u8`` (arcq_linear_kernel.cu:280-340): one-byte codes on both sides.
+    The bit width is the table's: L x L entries <-> log2 L bits.  Codes are packed and the packed kernel runs."""
+    L = int(product_table.shape[0])
+    bits = L.bit_length() - 1
+    if 2 ** bits != L or bits not in (2, 3, 4):
+        raise RuntimeError(f"product_table of {L} levels: expected 4, 8 or 16")
+    return arcq_linear_forward_product_table(pack_codes(x_codes, bits), x_center, x_scale, x_code_sum,
+                                             pack_codes(w_codes, bits), w_center, w_scale, w_code_sum, product_table,
+                                             bias, bits, group_size, x_codes.shape[1], w_codes.shape[0])

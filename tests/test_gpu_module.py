@@ -135,3 +135,34 @@ def test_host_pipeline_returns_each_batch_in_order(pkg, cuda_device):
         assert torch.equal(g, w)
     assert pipe.run(iter([])) == 0
     assert pkg.ops.device_status() == 0
+
+
+@pytest.mark.parametrize("name", ["c1_w4a4", "c1_w3a3"])
+def test_operators_with_the_reference_extension_signatures(pkg, golden, cuda_device, name):
+    """The product-table and one-byte-code operator forms the reference module's ``packed`` and ``u8`` branches
+    call (arcq_packed_linear.py:177-213): same result as the two-codebook operator."""
+    g = golden(name)
+    dev, bits = cuda_device, g["bits"]
+    layer = pkg.ARCQPackedLinear(_source(pkg, g), "packed").to(dev)
+    x = torch.from_numpy(g["X"]).to(dev)
+    ops = pkg.ops
+    px, mu, sg, cs = ops.quantize_activation(x, layer.activation_thresholds, layer.activation_codebook, bits, 64)
+    want = ops.arcq_linear_forward(px, mu, sg, cs, layer.packed_weight_codes, layer.weight_center, layer.weight_scale,
+                                   layer.weight_code_sum, layer.activation_codebook, layer.weight_codebook, layer.bias,
+                                   bits, 64, g["K"], g["N"])
+    a_cb, w_cb = ops.codebooks_from_product_table(layer.product_table, px, cs, bits, 64)
+    assert torch.allclose(a_cb, layer.activation_codebook, rtol=1e-5, atol=1e-7)
+    assert torch.allclose(w_cb, layer.weight_codebook, rtol=1e-5, atol=1e-7)
+    rms = float(want.pow(2).mean().sqrt())
+    got = ops.arcq_linear_forward_product_table(px, mu, sg, cs, layer.packed_weight_codes, layer.weight_center,
+                                                layer.weight_scale, layer.weight_code_sum, layer.product_table,
+                                                layer.bias, bits, 64, g["K"], g["N"])
+    assert float((got - want).abs().max()) < 1e-3 * rms
+    xc, mu8, sg8, cs8 = ops.quantize_activation_u8(x, layer.activation_thresholds, layer.activation_codebook, bits, 64)
+    assert xc.dtype == torch.uint8 and tuple(xc.shape) == tuple(x.shape)
+    assert torch.equal(mu8, mu) and torch.equal(sg8, sg) and torch.equal(cs8, cs)
+    wc = ops.unpack_codes_u8(layer.packed_weight_codes, bits, g["K"])
+    got8 = ops.arcq_linear_forward_u8(xc, mu8, sg8, cs8, wc, layer.weight_center, layer.weight_scale,
+                                      layer.weight_code_sum, layer.product_table, layer.bias, 64)
+    assert float((got8 - want).abs().max()) < 1e-3 * rms
+    assert ops.device_status() == 0

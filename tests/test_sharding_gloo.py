@@ -77,3 +77,43 @@ def test_wrong_shard_size_is_rejected_on_the_host():
     res = dict(q.get(timeout=120) for _ in procs)
     [p.join(timeout=60) for p in procs]
     assert res == {0: "skipped", 1: "ValueError"}
+
+
+def _gatherer_worker(rank: int, world: int, port: int, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    pkg = entry.import_package()
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        B, C = 8, 5
+        g = pkg.sharding.LogitsGatherer(B, C, torch.float32, torch.device("cpu"))
+        ok = True
+        for step in range(3):                      # both staging rows and both result buffers get reused
+            s, e = pkg.sharding.shard_bounds(B, world, rank)
+            local = (torch.arange(s, e, dtype=torch.float32)[:, None] + 0.125 * torch.arange(C)) * (step + 1)
+            g.submit(local)
+            want = (torch.arange(B, dtype=torch.float32)[:, None] + 0.125 * torch.arange(C)) * (step + 1)
+            ok = ok and bool(torch.equal(g.result(), want))
+        try:
+            g.submit(torch.zeros(3, C))            # a rank that arrives with the wrong shard fails on the host
+            ok = False
+        except ValueError:
+            pass
+        q.put((rank, ok))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_logits_gatherer_two_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gatherer_worker, args=(r, 2, port, q)) for r in range(2)]
+    [p.start() for p in procs]
+    res = dict(q.get(timeout=120) for _ in procs)
+    [p.join(timeout=60) for p in procs]
+    assert res == {0: True, 1: True}
+
+
+def test_logits_gatherer_refuses_uneven_shards(pkg):
+    with pytest.raises(RuntimeError):
+        pkg.sharding.LogitsGatherer(8, 5, torch.float32, torch.device("cpu")).result()
