@@ -74,7 +74,7 @@ enum Opt {
   O_WS_BN, O_WS_SA, O_WS_WS, O_WS_STATIONARY, O_WS_NBB, O_WS_GRID, O_WS_TMA_STORE, O_WS_ROTATE,
   O_ACT_QUANT_V1, O_ACT_QUANT_V2, O_LN_PLAIN,
   O_PAIR, O_PAIR_MIN_M, O_PAIR_BN, O_PAIR_SA, O_PAIR_KS, O_PAIR_NBB, O_PAIR_LUT, O_PAIR_PAIRS, O_PAIR_STATIONARY,
-  O_PAIR_WS, O_PAIR_FLAGS, O_PDL, O_POLL_LIMIT, O_SPIN_LIMIT, O_COUNT
+  O_PAIR_WS, O_PDL, O_POLL_LIMIT, O_SPIN_LIMIT, O_COUNT
 };
 struct OptDef { const char* name; int dflt; };
 const OptDef kOptDefs[O_COUNT] = {
@@ -83,7 +83,7 @@ const OptDef kOptDefs[O_COUNT] = {
     {"ARCQ_ACT_QUANT_V1", 0}, {"ARCQ_ACT_QUANT_V2", 0},   {"ARCQ_LN_PLAIN", 0},
     {"ARCQ_PAIR", 1},         {"ARCQ_PAIR_MIN_M", 1024},  {"ARCQ_PAIR_BN", 0},     {"ARCQ_PAIR_SA", 0},
     {"ARCQ_PAIR_KS", 0},      {"ARCQ_PAIR_NBB", 0},       {"ARCQ_PAIR_LUT", 0},    {"ARCQ_PAIR_PAIRS", 0},
-    {"ARCQ_PAIR_STATIONARY", -1}, {"ARCQ_PAIR_WS", 0}, {"ARCQ_PAIR_FLAGS", 0}, {"ARCQ_PDL", 1},
+    {"ARCQ_PAIR_STATIONARY", -1}, {"ARCQ_PAIR_WS", 0}, {"ARCQ_PDL", 1},
     {"ARCQ_POLL_LIMIT", 1 << 21}, {"ARCQ_SPIN_LIMIT", 1 << 25},
 };
 int g_opt[O_COUNT];
@@ -780,8 +780,6 @@ static int launch_pair_gemm(const PairConfig& cfg, const void* xhat, const void*
   p.y_f32 = (y_dtype == ARCQ_DT_F32) ? 1 : 0;
   p.poll_limit = static_cast<uint32_t>(opt(O_POLL_LIMIT));
   p.spin_limit = static_cast<uint32_t>(opt(O_SPIN_LIMIT));
-  p.trace = g_trace_buf;
-  p.flags = opt(O_PAIR_FLAGS);
   p.status = status_ptr();
   if (p.status == nullptr) return fail(ARCQ_E_CUDA, "device status word not reachable");
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -55,8 +55,6 @@ struct PairParams {
   int y_f32;
   uint32_t poll_limit;  // sleeping waits give up after this many polls
   uint32_t spin_limit;  // the issuing thread's busy waits give up after this many probes
-  long long* trace;     // debugging: 256 time stamps per CTA, or null
-  int flags;            // timing experiments (wrong results): 1 no output stores, 2 epilogue only hands the accumulator back
   int* status;
 };
 
@@ -310,8 +308,6 @@ struct PairBuildCtx {
   uint32_t wtile_bytes, lut_shift, w_full_leader, w_empty, poll_limit;
   int G, hb, ws, n_builders;
   bool stationary;
-  long long* tr;           // debugging time stamps of this CTA, or null
-  int tr_base;
 };
 
 // Rebuild the sub-tiles of jobs first, first + stride, ... (< n_jobs; job j is group j % G) with the 256 threads
@@ -331,14 +327,6 @@ __device__ __forceinline__ bool pair_build_jobs(const PairBuildCtx& c, int bt, i
   uint32_t ca0[kPairJobBlock][kPairMaxUnits], ca1[kPairJobBlock][kPairMaxUnits];
   uint32_t cb0[kPairJobBlock][kPairMaxUnits], cb1[kPairJobBlock][kPairMaxUnits];
   bool ok = true;
-  int n_done = 0;
-  auto bstamp = [&](int slot) {
-    if (c.tr != nullptr && bt == 0 && slot < 24) {
-      long long t;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-      c.tr[c.tr_base + slot] = t;
-    }
-  };
   auto load_block = [&](int j0, uint32_t (&c0)[kPairJobBlock][kPairMaxUnits], uint32_t (&c1)[kPairJobBlock][kPairMaxUnits]) {
 #pragma unroll
     for (int jj = 0; jj < kPairJobBlock; ++jj) {
@@ -409,7 +397,6 @@ __device__ __forceinline__ bool pair_build_jobs(const PairBuildCtx& c, int bt, i
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(c.w_full_leader + wslot * 8);
-      bstamp(++n_done);
     }
   };
   const int blk = kPairJobBlock * stride;
@@ -417,7 +404,6 @@ __device__ __forceinline__ bool pair_build_jobs(const PairBuildCtx& c, int bt, i
   load_block(first + blk, cb0, cb1);
   // the pair table and the folded statistics are complete (all builder threads of the CTA)
   if (sync_first) asm volatile("bar.sync 1, %0;" ::"r"(c.n_builders) : "memory");
-  bstamp(0);
   for (int j0 = first; j0 < n_jobs && ok; j0 += 2 * blk) {
     build_block(j0, ca0, ca1);
     load_block(j0 + 2 * blk, ca0, ca1);
@@ -499,18 +485,6 @@ packed_weight_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const _
   tc_fence_after_sync();
   const uint32_t tmem_base = *s_tmem;
   bool ok = true;
-  long long* const tr = (p.trace != nullptr) ? p.trace + static_cast<long long>(blockIdx.x) * 256 : nullptr;
-  auto stamp = [&](int slot) {     // debugging only, outside the per-stage loops
-    if (tr != nullptr && slot < 256) {
-      long long t;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-      tr[slot] = t;
-    }
-  };
-  auto cstamp = [&](int slot) {   // debugging: cycle counter of this SM
-    if (tr != nullptr && slot < 256) tr[slot] = clock64();
-  };
-  if (tid == 0) stamp(0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA: this CTA's half of every A tile
@@ -602,7 +576,6 @@ packed_weight_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const _
             if (++slot == sa) { slot = 0; ph ^= 1; a_lo = a_lo0; }
           }
           buf ^= 1;
-          if (lane == 0 && t < 8) stamp(120 + t);
           if (__any_sync(0xffffffffu, good == 0)) break;
         }
       } else {
@@ -722,16 +695,12 @@ packed_weight_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const _
       c.poll_limit = poll_limit;
       c.G = G; c.hb = hb; c.ws = p.ws; c.n_builders = n_builders;
       c.stationary = stationary;
-      c.tr = tr;
-      c.tr_base = is_epi ? 224 : 200;
       // A slab that is walked once (stationary, or a streaming ring with a single batch of tiles) is built while
       // the epilogue warps have nothing to drain yet: the two groups alternate on its sub-tiles (each sub-tile is
       // still the work of eight warps).  A ring that is walked several times is rebuilt by the weight warps alone.
       if (stationary || fills == 1) ok = pair_build_jobs<BITS>(c, bt, lane, is_epi ? 1 : 0, 2, fills * G, true);
       else if (!is_epi) ok = pair_build_jobs<BITS>(c, bt, lane, 0, 1, fills * G, true);
       else asm volatile("bar.sync 1, %0;" ::"r"(n_builders) : "memory");   // only orders the table fill above
-      if (tid == 2 * 32) stamp(8);
-      if (tid == (2 + kPairEpiWarps) * 32) stamp(9);
     }
     if (is_epi) {
       // ---------------------------------------------------------------- epilogue (own 128 rows of each tile)
@@ -792,7 +761,6 @@ packed_weight_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const _
         const uint32_t buf = static_cast<uint32_t>(t) & 1;
         if (!mbar_wait_sleep_a(acc_full + buf * 8, (static_cast<uint32_t>(t) >> 1) & 1, poll_limit, 32)) { ok = false; break; }
         tc_fence_after_sync();
-        if (ew == 0 && lane == 0 && t < 20) stamp(160 + 2 * t);
         const int row0 = row_of(t) + lq * 32;
         const uint32_t t_row = tmem_base + buf * 256 + (static_cast<uint32_t>(lq * 32) << 16);
         const bool live = row0 < p.M;     // some of these 32 rows are inside the matrix
@@ -825,7 +793,6 @@ packed_weight_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const _
           }
         }
         if (!released) release();
-        if (ew == 0 && lane == 0 && t < 20) stamp(161 + 2 * t);
       }
       if (lane == 0) tma_store_wait_all();
     }

@@ -74,7 +74,7 @@ int arcq_debug_trace(void* device_buffer);
  * at any time (process-wide).  Names: ARCQ_WS_BN, ARCQ_WS_SA, ARCQ_WS_WS, ARCQ_WS_STATIONARY, ARCQ_WS_NBB,
  * ARCQ_WS_GRID, ARCQ_WS_TMA_STORE, ARCQ_WS_ROTATE, ARCQ_ACT_QUANT_V1, ARCQ_ACT_QUANT_V2, ARCQ_LN_PLAIN,
  * ARCQ_PAIR, ARCQ_PAIR_MIN_M, ARCQ_PAIR_BN, ARCQ_PAIR_SA, ARCQ_PAIR_KS, ARCQ_PAIR_NBB, ARCQ_PAIR_LUT,
- * ARCQ_PAIR_PAIRS, ARCQ_PAIR_STATIONARY, ARCQ_PAIR_WS, ARCQ_PAIR_FLAGS, ARCQ_PDL, ARCQ_POLL_LIMIT,
+ * ARCQ_PAIR_PAIRS, ARCQ_PAIR_STATIONARY, ARCQ_PAIR_WS, ARCQ_PDL, ARCQ_POLL_LIMIT,
  * ARCQ_SPIN_LIMIT.  Normal use sets none.
  * Unknown names return ARCQ_E_BAD_ARG.  No reference counterpart.
  */
