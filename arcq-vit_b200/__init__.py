@@ -3,7 +3,8 @@
 The directory name carries a hyphen; import it through ``__graft_entry__.import_package()``
 (or any ``importlib`` loader that registers it as ``arcq_vit_b200``).
 """
-from . import _cabi, codebook, ops, packing, sharding  # noqa: F401
+from . import _cabi, codebook, ops, packing, sharding, staging  # noqa: F401
+from .staging import WeightStager, attach_weight_stager  # noqa: F401
 from .convert import (convert_arcq_linear_to_packed, count_packed_linear, load_packed_state_dict,  # noqa: F401
                       to_on_the_fly)
 from .packed_linear import ARCQPackedLinear, ARCQPackedLinearOnTheFly, quantize_weight  # noqa: F401

@@ -16,6 +16,7 @@ import torch
 import torch.nn as nn
 
 from .packed_linear import ARCQPackedLinear, ARCQPackedLinearOnTheFly
+from .staging import attach_weight_stager
 
 
 def _is_pcarcq_linear(module: nn.Module) -> bool:
@@ -37,13 +38,20 @@ def count_packed_linear(model: nn.Module) -> int:
     return sum(1 for m in model.modules() if isinstance(m, (ARCQPackedLinear, ARCQPackedLinearOnTheFly)))
 
 
-def to_on_the_fly(model: nn.Module) -> nn.Module:
-    """Replace every ARCQPackedLinear by an ARCQPackedLinearOnTheFly sharing its buffers."""
+def _swap_to_on_the_fly(model: nn.Module) -> None:
     for name, child in list(model.named_children()):
         if isinstance(child, ARCQPackedLinear):
             setattr(model, name, ARCQPackedLinearOnTheFly.from_packed(child))
         else:
-            to_on_the_fly(child)
+            _swap_to_on_the_fly(child)
+
+
+def to_on_the_fly(model: nn.Module) -> nn.Module:
+    """Replace every ARCQPackedLinear by an ARCQPackedLinearOnTheFly sharing its buffers, and give the new
+    layers a common weight stager (staging.py) so that each layer's weight is unpacked while the previous
+    layer computes."""
+    _swap_to_on_the_fly(model)
+    attach_weight_stager(model)
     return model
 
 
@@ -77,4 +85,6 @@ def load_packed_state_dict(model: nn.Module, state_dict: Dict[str, torch.Tensor]
     if strict and (missing or unexpected):
         raise KeyError(f"packed checkpoint mismatch: missing={missing[:5]} unexpected={unexpected[:5]}")
     model.load_state_dict({k: v for k, v in rest.items() if k in own}, strict=False)
+    if on_the_fly:
+        attach_weight_stager(model)
     return model

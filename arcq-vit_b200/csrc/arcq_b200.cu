@@ -19,7 +19,9 @@
 #include "packed_gemm.cuh"
 #include "gemm_ws.cuh"
 #include "gemm_pair.cuh"
+#include "gemm_pair_dense.cuh"
 #include "add_layernorm.cuh"
+#include "ln_act_quant.cuh"
 #include <cudaTypedefs.h>
 
 namespace {
@@ -529,6 +531,100 @@ bool choose_pair_config(long long M, long long N, long long K, int bits, bool y_
   return true;
 }
 
+
+// ---- dense-weight CTA-pair kernel: configuration ----
+struct PairDenseConfig {
+  int bn, sa, ks, pairs;
+  size_t smem;
+};
+
+int max_resident_dense_pairs(size_t smem) {
+  static thread_local int cached_dev = -1, cached = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev == cached_dev && cached > 0) return cached;
+  int n = 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(sm_count() / 2 * 2));
+  cfg.blockDim = dim3(arcq::kPairDenseThreads);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, arcq::dense_weight_gemm_pair_kernel, &cfg);
+  if (e != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    n = sm_count() / 2;
+  }
+  if (n > sm_count() / 2) n = sm_count() / 2;
+  cached = n;
+  cached_dev = dev;
+  return n;
+}
+
+// Slab width, stages and grid for the dense-weight pair kernel; false leaves the shape to the one-CTA kernel.
+// Cost model in microseconds, same constants as the packed-weight pair kernel's: a tile is bound by its output
+// stores (about 22 GB/s per SM) or by the issuing thread, and every slab streams the whole activation from L2.
+bool choose_pair_dense_config(long long M, long long N, long long K, bool y_f32, PairDenseConfig* c) {
+  if (opt(O_PAIR) == 0 || M < opt(O_PAIR_MIN_M)) return false;
+  const int G = static_cast<int>(K / 64);
+  if (G < 1) return false;
+  const long long tiles_m = (M + arcq::kPairTileM - 1) / arcq::kPairTileM;
+  const size_t full_smem = kSmemBudget + 1024;
+  {
+    static thread_local int done_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (done_dev != dev) {
+      if (cudaFuncSetAttribute(arcq::dense_weight_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(full_smem)) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+      }
+      done_dev = dev;
+    }
+  }
+  int max_pairs = max_resident_dense_pairs(full_smem);
+  if (opt(O_PAIR_PAIRS) > 0 && opt(O_PAIR_PAIRS) < max_pairs) max_pairs = opt(O_PAIR_PAIRS);
+  static const int cand[] = {256, 192, 160, 128, 96, 64, 32};
+  double best_cost = 0;
+  bool found = false;
+  PairDenseConfig best = {};
+  for (int bn : cand) {
+    if (N % bn != 0) continue;
+    if (opt(O_PAIR_BN) > 0 && bn != opt(O_PAIR_BN)) continue;
+    const long long slabs = N / bn;
+    if (slabs > max_pairs) continue;
+    long long per = max_pairs / slabs;
+    if (per > tiles_m) per = tiles_m;
+    const long long tiles_pp = (tiles_m + per - 1) / per;
+    PairDenseConfig k = {};
+    k.bn = bn; k.pairs = static_cast<int>(slabs * per);
+    k.ks = (G % 2 == 0) ? 2 : (G % 3 == 0) ? 3 : 1;
+    if (opt(O_PAIR_KS) > 0 && G % opt(O_PAIR_KS) == 0) k.ks = opt(O_PAIR_KS);
+    bool fits = false;
+    for (int sa = 16; sa >= 2 && !fits; --sa) {
+      if (opt(O_PAIR_SA) > 0 && sa != opt(O_PAIR_SA)) continue;
+      if (sa * k.ks > 8 && opt(O_PAIR_SA) == 0) continue;             // eight sub-stages in flight are plenty
+      const size_t need = arcq::pair_dense_smem_layout(bn, sa, k.ks).total;
+      if (need <= kSmemBudget) { k.sa = sa; k.smem = need + 1024; fits = true; }
+    }
+    if (!fits) continue;
+    const int esize = y_f32 ? 4 : 2;
+    const double t_write = 128.0 * bn * esize / 22.0e3;
+    const double t_issue = (G / k.ks) * (k.ks * 4 * (bn > 128 ? 0.056 * bn / 192.0 : 0.04) + 0.1);
+    const double t_l2 = static_cast<double>(slabs) * M * K * 2.0 / 5.0e6;
+    const double path = tiles_pp * ((t_write > t_issue ? t_write : t_issue) + 0.15);
+    const double cost = 1.5 + (path > t_l2 ? path : t_l2);
+    if (!found || cost < best_cost) { best = k; best_cost = cost; found = true; }
+  }
+  if (!found) return false;
+  *c = best;
+  return true;
+}
+
 }  // namespace
 
 extern "C" {
@@ -801,6 +897,36 @@ static int launch_pair_gemm(const PairConfig& cfg, const void* xhat, const void*
   return ARCQ_OK;
 }
 
+static int launch_pair_dense_gemm(const PairDenseConfig& cfg, const void* xhat, const void* w16, const float* bias,
+                                  int64_t M, int64_t N, int64_t K, void* y, int y_dtype, void* stream) {
+  CUtensorMap tm_a, tm_w, tm_y;
+  if (!make_tensor_map_2d(&tm_a, xhat, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, static_cast<uint64_t>(M),
+                          static_cast<uint64_t>(K), 64, arcq::kTileM, CU_TENSOR_MAP_SWIZZLE_128B))
+    return fail(ARCQ_E_CUDA, "cuTensorMapEncodeTiled failed for the activation matrix");
+  if (!make_tensor_map_2d(&tm_w, w16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, static_cast<uint64_t>(N),
+                          static_cast<uint64_t>(K), 64, cfg.bn / 2, CU_TENSOR_MAP_SWIZZLE_128B))
+    return fail(ARCQ_E_CUDA, "cuTensorMapEncodeTiled failed for the weight matrix");
+  const int out_cw = (y_dtype == ARCQ_DT_F32) ? 16 : 32;
+  if (!make_tensor_map_2d(&tm_y, y, (y_dtype == ARCQ_DT_F32) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                          (y_dtype == ARCQ_DT_F32) ? 4 : 2, static_cast<uint64_t>(M), static_cast<uint64_t>(N),
+                          out_cw, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+    return fail(ARCQ_E_CUDA, "cuTensorMapEncodeTiled failed for the output matrix");
+  arcq::PairDenseParams p;
+  p.bias = bias;
+  p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K); p.G = static_cast<int>(K / 64);
+  p.bn = cfg.bn; p.sa = cfg.sa; p.ks = cfg.ks;
+  p.y_f32 = (y_dtype == ARCQ_DT_F32) ? 1 : 0;
+  p.poll_limit = static_cast<uint32_t>(opt(O_POLL_LIMIT));
+  p.spin_limit = static_cast<uint32_t>(opt(O_SPIN_LIMIT));
+  p.status = status_ptr();
+  if (p.status == nullptr) return fail(ARCQ_E_CUDA, "device status word not reachable");
+  launch_pdl(arcq::dense_weight_gemm_pair_kernel, static_cast<unsigned>(2 * cfg.pairs), arcq::kPairDenseThreads, cfg.smem,
+             static_cast<cudaStream_t>(stream), tm_a, tm_w, tm_y, p);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "dense_weight_gemm (pair) launch");
+  return ARCQ_OK;
+}
+
 int arcq_packed_weight_gemm(const void* xhat, const uint8_t* packed_w, const float* mu_w, const float* sigma_w,
                             const float* codesum_w, const float* w_codebook, const float* bias, int bits,
                             int group_size, int64_t M, int64_t N, int64_t K, void* y, int y_dtype, void* stream) {
@@ -841,6 +967,9 @@ int arcq_dense_weight_gemm(const void* xhat, const void* w16, const float* bias,
   if (!aligned(xhat, 16) || !aligned(w16, 16) || !aligned(y, 16))
     return fail(ARCQ_E_ALIGN, "xhat, w16 and y must be 16-byte aligned");
   if (M == 0) return ARCQ_OK;
+  PairDenseConfig pc;
+  if (choose_pair_dense_config(M, N, K, y_dtype == ARCQ_DT_F32, &pc))
+    return launch_pair_dense_gemm(pc, xhat, w16, bias, M, N, K, y, y_dtype, stream);
   return launch_ws_gemm(true, xhat, w16, nullptr, nullptr, nullptr, nullptr, bias, 4, M, N, K, y, y_dtype, stream);
 }
 
@@ -873,6 +1002,54 @@ int arcq_add_layernorm(const void* x, const void* y, const float* gamma, const f
   return ARCQ_OK;
 }
 
+int arcq_add_layernorm_act_quant(const void* x, const void* y, const float* gamma, const float* beta, float eps,
+                                 int64_t M, int64_t K, const float* thresholds, const float* codebook, int bits,
+                                 int group_size, void* sum_out, void* h_out, void* xhat, void* stream) {
+  if (x == nullptr || gamma == nullptr || beta == nullptr || thresholds == nullptr || codebook == nullptr || xhat == nullptr)
+    return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
+  if (group_size != 64) return fail(ARCQ_E_UNSUPPORTED, "group_size %d: only 64 is built", group_size);
+  if (M < 0 || K <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape M=%lld K=%lld", (long long)M, (long long)K);
+  if (K % 64 != 0) return fail(ARCQ_E_BAD_SHAPE, "K=%lld is not a multiple of the group size 64", (long long)K);
+  if (K / 64 > arcq::kLnqMaxG) return fail(ARCQ_E_TOO_LARGE, "rows longer than %d values are not built", 64 * arcq::kLnqMaxG);
+  if (y == nullptr && sum_out != nullptr) return fail(ARCQ_E_BAD_ARG, "sum_out without y");
+  if (!aligned(x, 16) || !aligned(xhat, 16) || (y != nullptr && !aligned(y, 16)) ||
+      (sum_out != nullptr && !aligned(sum_out, 16)) || (h_out != nullptr && !aligned(h_out, 16)))
+    return fail(ARCQ_E_ALIGN, "all matrices must be 16-byte aligned");
+  if (M == 0) return ARCQ_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int G = static_cast<int>(K / 64);
+  const int rows_per_tile = arcq::kLnqThreads / G;
+  const long long tiles = (M + rows_per_tile - 1) / rows_per_tile;
+  const long long cap = static_cast<long long>(sm_count()) * 4;
+  const unsigned grid = static_cast<unsigned>(tiles < cap ? tiles : cap);
+  const size_t smem = arcq::lnq_smem_bytes(G);
+  const __half *xh = static_cast<const __half*>(x), *yh = static_cast<const __half*>(y);
+  __half *so = static_cast<__half*>(sum_out), *ho = static_cast<__half*>(h_out), *xo = static_cast<__half*>(xhat);
+#define ARCQ_LAUNCH_LNQ(B, HASY)                                                                                       \
+  do {                                                                                                                 \
+    static thread_local int done_dev = -1;                                                                             \
+    int dev = 0;                                                                                                       \
+    cudaGetDevice(&dev);                                                                                               \
+    if (done_dev != dev) {                                                                                             \
+      cudaFuncSetAttribute(arcq::add_layernorm_act_quant_kernel<B, HASY>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           static_cast<int>(arcq::lnq_smem_bytes(arcq::kLnqMaxG)));                                    \
+      done_dev = dev;                                                                                                  \
+    }                                                                                                                  \
+    launch_pdl(arcq::add_layernorm_act_quant_kernel<B, HASY>, grid, arcq::kLnqThreads, smem, st, xh, yh, gamma, beta,  \
+               eps, static_cast<long long>(M), G, thresholds, codebook, so, ho, xo);                                   \
+  } while (0)
+  if (y != nullptr) {
+    if (bits == 4) ARCQ_LAUNCH_LNQ(4, true); else if (bits == 3) ARCQ_LAUNCH_LNQ(3, true); else ARCQ_LAUNCH_LNQ(2, true);
+  } else {
+    if (bits == 4) ARCQ_LAUNCH_LNQ(4, false); else if (bits == 3) ARCQ_LAUNCH_LNQ(3, false); else ARCQ_LAUNCH_LNQ(2, false);
+  }
+#undef ARCQ_LAUNCH_LNQ
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "add_layernorm_act_quant launch");
+  return ARCQ_OK;
+}
+
 int arcq_unpack_codes(const uint8_t* packed, int64_t rows, int64_t length, int bits, uint8_t* codes_out, void* stream) {
   if (!packed || !codes_out) return fail(ARCQ_E_BAD_ARG, "null pointer argument");
   if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
@@ -896,6 +1073,27 @@ int arcq_pack_codes(const uint8_t* codes, int64_t rows, int64_t length, int bits
       codes, rows, length, pc, bits, packed_out);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "pack launch");
+  return ARCQ_OK;
+}
+
+int arcq_unpack_weight_f16(const uint8_t* packed, const float* mu, const float* sigma, const float* codesum,
+                           const float* codebook, int bits, int group_size, int64_t rows, int64_t K, void* out,
+                           void* stream) {
+  if (!packed || !mu || !sigma || !codesum || !codebook || !out) return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
+  if (group_size != 64) return fail(ARCQ_E_UNSUPPORTED, "group_size %d: only 64 is built", group_size);
+  if (rows < 0 || K <= 0 || K % 64 != 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape rows=%lld K=%lld", (long long)rows, (long long)K);
+  if (!aligned(packed, 4) || !aligned(out, 16)) return fail(ARCQ_E_ALIGN, "packed codes must be 4-byte, out 16-byte aligned");
+  if (rows == 0) return ARCQ_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(rows * (K / 8), 256, 8);
+  const int k = static_cast<int>(K);
+  __half* o = static_cast<__half*>(out);
+  if (bits == 4) arcq::unpack_weight_f16_kernel<4><<<grid, 256, 0, st>>>(packed, mu, sigma, codesum, codebook, rows, k, o);
+  else if (bits == 3) arcq::unpack_weight_f16_kernel<3><<<grid, 256, 0, st>>>(packed, mu, sigma, codesum, codebook, rows, k, o);
+  else arcq::unpack_weight_f16_kernel<2><<<grid, 256, 0, st>>>(packed, mu, sigma, codesum, codebook, rows, k, o);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "unpack_weight_f16 launch");
   return ARCQ_OK;
 }
 

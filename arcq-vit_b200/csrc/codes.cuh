@@ -101,4 +101,41 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ packed, const float* 
   }
 }
 
+// out[r, k] = fp16(mu' + sigma16 * cb16[c]) with mu' = fp16(mu - sigma*codesum/64), sigma16 = fp16(sigma),
+// cb16 = fp16(cb[c]) and one half-precision fused multiply-add: bit for bit the weight the packed-weight
+// GEMM kernels rebuild in shared memory, written out so that a dense GEMM can read it by TMA.
+// One thread per chunk of 8 codes (16 bytes of output); groups of 64.
+template <int BITS>
+__global__ void unpack_weight_f16_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ mu,
+                                         const float* __restrict__ sigma, const float* __restrict__ codesum,
+                                         const float* __restrict__ codebook, long long rows, int K,
+                                         __half* __restrict__ out) {
+  __shared__ __half s_cb[16];
+  if (threadIdx.x < 16) s_cb[threadIdx.x] = __float2half_rn((threadIdx.x < (1 << BITS)) ? codebook[threadIdx.x] : 0.0f);
+  __syncthreads();
+  const int chunks = K / 8;
+  const int G = K / 64;
+  const long long pc = static_cast<long long>(K) * BITS / 8;
+  const long long total = rows * chunks;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / chunks;
+    const int ch = static_cast<int>(i - r * chunks);
+    const int g = ch >> 3;
+    const uint32_t w = load_codes8<BITS>(packed + r * pc, ch);
+    const float sg = __ldg(sigma + r * G + g);
+    const __half2 f2 = __floats2half2_rn(sg, fmaf(-sg, __ldg(codesum + r * G + g) * (1.0f / 64.0f), __ldg(mu + r * G + g)));
+    const __half2 s2 = __low2half2(f2), m2 = __high2half2(f2);
+    uint32_t h[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const __half2 v2 = __halves2half2(s_cb[(w >> (8 * q)) & 15u], s_cb[(w >> (8 * q + 4)) & 15u]);
+      const __half2 r2 = __hfma2(s2, v2, m2);
+      h[q] = *reinterpret_cast<const uint32_t*>(&r2);
+    }
+    *reinterpret_cast<uint4*>(out + r * K + ch * 8) = make_uint4(h[0], h[1], h[2], h[3]);
+  }
+}
+
+
 }  // namespace arcq

@@ -1,0 +1,306 @@
+// Residual add + LayerNorm + activation quantizer in one pass over fp16 rows: the glue in front of the first
+// packed linear of a sub-block (norm1 -> qkv, norm2 -> fc1) merged with that linear's input quantizer.
+//   s    = fp16(x + y)                                    (written out when y is given: the residual stream)
+//   h    = fp16((s - mean(s)) * rsqrt(var(s) + eps) * gamma + beta)     (never written, unless asked for)
+//   xhat = fp16(reconstruction of the ARCQ quantization of h in groups of 64)
+// The separate kernels write h and read it back; here it stays in registers.
+//
+// Layout: one thread per 64-value group, as in the staged quantizer (act_quant_v2.cuh, which documents the
+// summation order, the division-free exact threshold test and the first-guess grid used below).  A tile is
+// R whole rows (R * K/64 <= 128 groups); x and y tiles are staged through shared memory with 16-byte
+// cp.async, the LayerNorm statistics of a row are the sums of its K/64 threads' partial sums, combined
+// through shared memory in a fixed order, so a row's result does not depend on the tile it falls in.
+// The quantizer part takes the fp16-rounded h, i.e. exactly what the separate quantizer kernel would read:
+// given the same h both produce the same bits.
+#pragma once
+#include <cuda_fp16.h>
+#include "ptx.cuh"
+#include "act_quant.cuh"
+#include "act_quant_v2.cuh"
+
+namespace arcq {
+
+constexpr int kLnqThreads = 128;
+constexpr int kLnqPitch = 144;      // bytes between staged group rows (128 data bytes, conflict-free pitch)
+constexpr int kLnqMaxG = 16;        // rows of up to 1024 values
+
+__host__ __device__ constexpr size_t lnq_smem_bytes(int G) {
+  return 2 * kLnqThreads * kLnqPitch            // x / residual-sum rows, y / reconstruction rows
+         + 16 * kLnqThreads * 4                 // per-thread limit columns
+         + 2 * kLnqThreads * 4                  // partial sums, partial sums of squares
+         + static_cast<size_t>(G) * 65 * 8      // (gamma, beta) pairs, one padded row of 65 per group
+         + 4 * 16 * 4 + kAq2Cells * 4 + 16;     // thresholds, half-gaps, codebook, grid positions, first guesses
+}
+
+template <int BITS, bool HAS_Y>
+__global__ void __launch_bounds__(kLnqThreads, 4)
+    add_layernorm_act_quant_kernel(const __half* __restrict__ x, const __half* __restrict__ y,
+                                   const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
+                                   long long M, int G, const float* __restrict__ thresholds,
+                                   const float* __restrict__ codebook, __half* __restrict__ sum_out,
+                                   __half* __restrict__ h_out, __half* __restrict__ xhat) {
+  pdl_launch_dependents();   // the next kernel of the stream may start its set-up
+
+  constexpr int L = 1 << BITS;
+  constexpr int kTableStride = kLnqThreads;
+  extern __shared__ __align__(16) uint8_t lnq_smem[];
+  uint8_t* const s_a = lnq_smem;                                          // x, then s = x + y
+  uint8_t* const s_b = s_a + kLnqThreads * kLnqPitch;                     // y, then the reconstruction
+  float* const s_table = reinterpret_cast<float*>(s_b + kLnqThreads * kLnqPitch);   // [16][128]
+  float* const s_p1 = s_table + 16 * kTableStride;                        // [128]
+  float* const s_p2 = s_p1 + kLnqThreads;                                 // [128]
+  float2* const s_gb = reinterpret_cast<float2*>(s_p2 + kLnqThreads);     // [G][65]
+  float* const s_th = reinterpret_cast<float*>(s_gb + G * 65);            // [16]
+  float* const s_h = s_th + 16;
+  float* const s_cb = s_h + 16;
+  float* const s_pos = s_cb + 16;
+  int* const s_guess = reinterpret_cast<int*>(s_pos + 16);                // [kAq2Cells]
+  const int tid = threadIdx.x;
+  const int K = G * 64;
+  const int R = kLnqThreads / G;            // rows per tile
+  const int active = R * G;                 // threads that own a group
+  const int my_row = tid / G, my_g = tid - my_row * G;
+
+  // ---- per-block set-up (reads only this layer's constants, so it runs before the wait below)
+  int my_exact = 1;
+  if (tid < 16) {
+    float th = __int_as_float(0x7f800000), h = 0.0f;
+    if (tid < L - 1) {
+      th = thresholds[tid];
+      if (th == 0.0f) {
+        h = 0x1p-100f;
+      } else {
+        const int b = __float_as_int(th);
+        const float up = __int_as_float(th > 0.0f ? b + 1 : b - 1);
+        h = __fmul_rn(__fsub_rn(up, th), 0.5f);
+      }
+      my_exact = (th == 0.0f || fabsf(th) > 1.0e-15f) ? 1 : 0;
+    }
+    s_th[tid] = th;
+    s_h[tid] = h;
+    s_cb[tid] = tid < L ? codebook[tid] : 0.0f;
+  }
+  for (int i = tid; i < K; i += kLnqThreads) s_gb[(i >> 6) * 65 + (i & 63)] = make_float2(__ldg(gamma + i), __ldg(beta + i));
+  const bool exact_r = __syncthreads_and(my_exact) != 0;
+  float grid_scale = 0.0f, grid_off = 0.0f;
+  bool use_guess = false;
+  if (L >= 4) {
+    const float th_first = s_th[0], th_last = s_th[L - 2];
+    grid_scale = static_cast<float>(kAq2Cells - 2) / (th_last - th_first);
+    grid_off = 1.0f - th_first * grid_scale;
+    int gap_ok = 1;
+    if (tid < 16) {
+      const float pos = tid < L - 1 ? fmaf(s_th[tid], grid_scale, grid_off) : __int_as_float(0x7f800000);
+      s_pos[tid] = pos;
+      if (tid < L - 2) gap_ok = (fmaf(s_th[tid + 1], grid_scale, grid_off) - pos > 1.1f) ? 1 : 0;
+    }
+    use_guess = __syncthreads_and(gap_ok) != 0 && exact_r && isfinite(grid_scale);
+    for (int k = tid; k < kAq2Cells; k += kLnqThreads) {
+      const float lim = static_cast<float>(k) - 0.05f;
+      int c = (s_pos[7] < lim) ? 8 : 0;
+      c += (s_pos[c + 3] < lim) ? 4 : 0;
+      c += (s_pos[c + 1] < lim) ? 2 : 0;
+      c += (s_pos[c] < lim) ? 1 : 0;
+      s_guess[k] = c * (kLnqThreads * 4);
+    }
+  }
+  float* const my_table = s_table + tid;
+  const char* const col = reinterpret_cast<const char*>(my_table);
+  constexpr int kStep = kTableStride * 4;
+  static_assert(kStep == 512, "the code extraction below assumes a 512-byte table step");
+  const float2* const my_gb = s_gb + my_g * 65;
+  const float inv_k = 1.0f / static_cast<float>(K);
+
+  pdl_wait();                // x and y may be the previous kernels' outputs
+
+  const long long tiles = (M + R - 1) / R;
+  for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const long long row0 = tile * R;
+    const int rows = static_cast<int>(min(static_cast<long long>(R), M - row0));
+    const int ngroups = rows * G;
+    // ---- stage the tile: rows are contiguous in memory, so the tile is one run of 128-byte group rows
+    {
+      const int nchunks = ngroups * 8;
+      const uint8_t* xs = reinterpret_cast<const uint8_t*>(x + row0 * K);
+      const uint8_t* ys = HAS_Y ? reinterpret_cast<const uint8_t*>(y + row0 * K) : nullptr;
+      const uint32_t da = smem_u32(s_a), db = smem_u32(s_b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int q = tid + kLnqThreads * i;
+        if (q < nchunks) {
+          cp_async16(da + (q >> 3) * kLnqPitch + (q & 7) * 16, xs + q * 16);
+          if (HAS_Y) cp_async16(db + (q >> 3) * kLnqPitch + (q & 7) * 16, ys + q * 16);
+        }
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    const bool valid = tid < ngroups;
+    uint8_t* const row_a = s_a + tid * kLnqPitch;
+    uint8_t* const row_b = s_b + tid * kLnqPitch;
+    float v[64];
+    if (valid) {
+      aq2_load_row<__half>(row_a, v);
+      if (HAS_Y) {
+        // s = fp16(x + y): the sum a separate add would store, written back over the staged x row
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 u = *reinterpret_cast<const uint4*>(row_b + 16 * c);
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+            const __half2 s2 = __floats2half2_rn(v[8 * c + 2 * j] + f.x, v[8 * c + 2 * j + 1] + f.y);
+            o[j] = *reinterpret_cast<const uint32_t*>(&s2);
+            const float2 fs = __half22float2(s2);
+            v[8 * c + 2 * j] = fs.x;
+            v[8 * c + 2 * j + 1] = fs.y;
+          }
+          *reinterpret_cast<uint4*>(row_a + 16 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) v[j] = 0.0f;
+    }
+
+    // ---- LayerNorm statistics of the row: two passes, partial sums of the row's G threads added in group order
+    {
+      float p[8];
+#pragma unroll
+      for (int l = 0; l < 8; ++l) p[l] = ((v[l] + v[8 + l]) + (v[16 + l] + v[24 + l])) + ((v[32 + l] + v[40 + l]) + (v[48 + l] + v[56 + l]));
+      s_p1[tid] = ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));
+    }
+    __syncthreads();
+    float mean_ln = 0.0f;
+    if (valid) {
+      const float* pr = s_p1 + my_row * G;
+      for (int g = 0; g < G; ++g) mean_ln += pr[g];
+      mean_ln *= inv_k;
+    }
+    {
+      float p[8];
+#pragma unroll
+      for (int l = 0; l < 8; ++l) {
+        p[l] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const float d = v[8 * c + l] - mean_ln;
+          p[l] = fmaf(d, d, p[l]);
+        }
+      }
+      s_p2[tid] = ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));
+    }
+    __syncthreads();
+    if (valid) {
+      float sq = 0.0f;
+      const float* pr = s_p2 + my_row * G;
+      for (int g = 0; g < G; ++g) sq += pr[g];
+      const float rstd = rsqrtf(sq * inv_k + eps);
+      // h in fp16, as the LayerNorm kernel stores it; from here on v holds what the quantizer would read
+#pragma unroll
+      for (int j = 0; j < 64; j += 2) {
+        const float2 gb0 = my_gb[j], gb1 = my_gb[j + 1];
+        const __half2 h2 = __floats2half2_rn((v[j] - mean_ln) * rstd * gb0.x + gb0.y, (v[j + 1] - mean_ln) * rstd * gb1.x + gb1.y);
+        const float2 f = __half22float2(h2);
+        v[j] = f.x;
+        v[j + 1] = f.y;
+      }
+      if (h_out != nullptr) {
+        __half* ho = h_out + (row0 + my_row) * K + my_g * 64;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t o[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o[j] = aq2_pack2<__half>(v[8 * c + 2 * j], v[8 * c + 2 * j + 1]);
+          *reinterpret_cast<uint4*>(ho + 8 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+
+    // ---- the activation quantizer on h (same steps as act_quant_v2_kernel)
+    const float mean = __fdiv_rn(sum64_ref_order(v), 64.0f);
+    float var;
+    {
+      float q[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        v[j] = __fsub_rn(v[j], mean);
+        q[j] = __fmul_rn(v[j], v[j]);
+      }
+      var = __fdiv_rn(sum64_ref_order(q), 64.0f);
+    }
+    const float scale = __fsqrt_rn(__fadd_rn(var, 1.0e-6f));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float t = __int_as_float(0x7f800000);
+      if (i < L - 1) {
+        const float th = s_th[i];
+        const float hs = __fmul_rd(__fmul_rn(s_h[i], scale), th == 0.0f ? 0x1p-50f : 1.0f);
+        t = exact_r ? __fmaf_rd(th, scale, hs) : th;
+      }
+      if (i < L) my_table[i * kTableStride] = t;
+    }
+    const char* const cbp = reinterpret_cast<const char*>(s_cb);
+    if (use_guess) {
+      const float inv = grid_scale * __frcp_rn(scale);
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        const float r = v[j];
+        const unsigned cell = min(__float2uint_rz(fmaf(r, inv, grid_off)), static_cast<unsigned>(kAq2Cells - 1));
+        int off = s_guess[cell];
+        off += (r > *reinterpret_cast<const float*>(col + off)) ? kStep : 0;
+        v[j] = *reinterpret_cast<const float*>(cbp + (off >> 7));          // code = off / 512, four bytes per entry
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        const float key = exact_r ? v[j] : __fdiv_rn(v[j], scale);
+        int off = 0;
+        if (BITS >= 4) off += (key > *reinterpret_cast<const float*>(col + off + 7 * kStep)) ? 8 * kStep : 0;
+        if (BITS >= 3) off += (key > *reinterpret_cast<const float*>(col + off + 3 * kStep)) ? 4 * kStep : 0;
+        off += (key > *reinterpret_cast<const float*>(col + off + 1 * kStep)) ? 2 * kStep : 0;
+        off += (key > *reinterpret_cast<const float*>(col + off)) ? kStep : 0;
+        v[j] = *reinterpret_cast<const float*>(cbp + (off >> 7));
+      }
+    }
+    const float code_sum = sum64_ref_order(v);
+    if (valid) {
+      // reconstruction mean + scale*(cb[c] - code_sum/64) in the reference's three rounded steps
+      const float vm = __fmul_rn(code_sum, 1.0f / 64.0f);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int e = 8 * c + 2 * j;
+          o[j] = aq2_pack2<__half>(__fadd_rn(mean, __fmul_rn(scale, __fsub_rn(v[e], vm))),
+                                   __fadd_rn(mean, __fmul_rn(scale, __fsub_rn(v[e + 1], vm))));
+        }
+        *reinterpret_cast<uint4*>(row_b + 16 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+    __syncthreads();
+    // ---- coalesced copy-out of the residual stream and the reconstruction
+    {
+      const int nchunks = ngroups * 8;
+      uint8_t* so = (HAS_Y && sum_out != nullptr) ? reinterpret_cast<uint8_t*>(sum_out + row0 * K) : nullptr;
+      uint8_t* xo = reinterpret_cast<uint8_t*>(xhat + row0 * K);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int q = tid + kLnqThreads * i;
+        if (q < nchunks) {
+          if (HAS_Y && so != nullptr)
+            *reinterpret_cast<uint4*>(so + q * 16) = *reinterpret_cast<const uint4*>(s_a + (q >> 3) * kLnqPitch + (q & 7) * 16);
+          *reinterpret_cast<uint4*>(xo + q * 16) = *reinterpret_cast<const uint4*>(s_b + (q >> 3) * kLnqPitch + (q & 7) * 16);
+        }
+      }
+    }
+    __syncthreads();   // the staging rows are free for the next tile
+  }
+}
+
+}  // namespace arcq

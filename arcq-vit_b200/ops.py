@@ -278,6 +278,29 @@ def dequant(packed, center, scale, code_sum, codebook, bits: int, group_size: in
     return out
 
 
+def unpack_weight_f16(packed, center, scale, code_sum, codebook, bits: int, group_size: int,
+                      out: torch.Tensor = None, stream: torch.cuda.Stream = None) -> torch.Tensor:
+    """Packed weight codes + statistics -> the fp16 matrix [N, K] the packed-weight GEMM kernels rebuild on chip
+    (same bits), for ``dense_weight_gemm``.  ``out``: scratch buffer of at least N*K fp16 values;
+    ``stream``: launch there instead of on the current stream."""
+    lib = _cabi.load()
+    packed = _dev(packed, "packed", torch.uint8)
+    center, scale, code_sum, codebook = (_dev(t, "stats", torch.float32) for t in (center, scale, code_sum, codebook))
+    R, G = center.shape
+    K = G * group_size
+    if out is not None:
+        if out.dtype != torch.float16 or not out.is_cuda or not out.is_contiguous() or out.numel() < R * K:
+            raise RuntimeError("out must be a contiguous CUDA fp16 buffer with at least R*K elements")
+        out = out.view(-1)[: R * K].view(R, K)
+    else:
+        out = torch.empty((R, K), dtype=torch.float16, device=packed.device)
+    handle = stream.cuda_stream if stream is not None else _stream()
+    _check(lib.arcq_unpack_weight_f16(packed.data_ptr(), center.data_ptr(), scale.data_ptr(), code_sum.data_ptr(),
+                                      codebook.data_ptr(), bits, group_size, R, K, out.data_ptr(), handle),
+           "arcq_unpack_weight_f16")
+    return out
+
+
 # ---------------------------------------------------------------------------------------------------------
 # The reference extension's exact operator signatures (arcq_infer_bind.cpp:57-66), for a shim that replaces
 # `fair_qat/arcq_infer_cuda/__init__.py` without touching the reference's module classes.

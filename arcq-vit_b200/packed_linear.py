@@ -259,9 +259,15 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
     # the module can apply the GELU that precedes it in an MLP block while it quantises its input
     supports_pre_gelu = True
 
-    # How the weight reaches the tensor cores.  "packed": rebuilt from the codes inside the GEMM kernel, never
-    # in HBM.  "dense": unpacked into an fp16 scratch matrix every forward (the reference's own data flow,
-    # arcq_packed_on_the_fly.py:147-160, with its `_weight_buffer`) and read by TMA.  "auto" is the packed form.
+    # How the weight reaches the tensor cores.
+    #   "staged": unpacked into one of two fp16 scratch matrices on a side stream while the previous layer runs
+    #             (the reference's own data flow, arcq_packed_on_the_fly.py:147-160, with its `_weight_buffer`),
+    #             then read by TMA.  Needs a WeightStager on the model (attached by this package's converters).
+    #   "packed": rebuilt from the codes inside the GEMM kernel, never in HBM.
+    #   "dense":  unpacked on the layer's own stream right before the GEMM (no overlap, no stager needed).
+    #   "auto":   staged when the model has a stager and the GEMM has at least WeightStager.min_rows rows, else packed.
+    # The three forms produce the same bits: the unpack kernel writes exactly the fp16 values the packed-weight
+    # kernels rebuild on chip.
     weight_form = os.environ.get("ARCQ_WEIGHT_FORM", "auto")
     _scratch: dict = {}
 
@@ -281,12 +287,14 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
             ARCQPackedLinearOnTheFly._scratch[key] = buf
         return buf
 
-    def _use_dense(self, rows: int) -> bool:
-        if self.weight_form == "dense":
-            return True
-        if self.weight_form == "packed":
-            return False
-        return False     # the two forms measured equal within 1 % on the DeiT shapes; the packed one needs no scratch
+    def _weight_route(self, rows: int) -> str:
+        form = self.weight_form
+        stager = getattr(self, "_stager", None)
+        if form == "auto":
+            return "staged" if stager is not None and rows >= stager.min_rows else "packed"
+        if form == "staged" and stager is None:
+            return "dense"
+        return form
 
     def forward(self, x: torch.Tensor, pre_gelu: bool = False) -> torch.Tensor:
         """``pre_gelu=True``: x is the pre-activation of the GELU in front of this layer; the result
@@ -299,12 +307,19 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
         if ops.packed_weight_gemm_supported(self.in_features, self.out_features, self.bits, self.group_size):
             # the reference's own data flow: fp16 activation quantised and reconstructed (its step 2),
             # then weight unpack + contraction + bias (its steps 3-5) in one persistent kernel
+            route = self._weight_route(x2.shape[0])
+            if route == "staged":
+                w16, ready = self._stager.stage(self)     # starts the next layer's unpack on the side stream too
             x_hat = ops.quantize_activation_dequant(x2, self.activation_thresholds, self.activation_codebook,
                                                     self.bits, self.group_size, torch.float16, pre_gelu)
-            if self._use_dense(x2.shape[0]):
-                w16 = ops.dequant(self.packed_weight_codes, self.weight_center, self.weight_scale,
-                                  self.weight_code_sum, self.weight_codebook, self.bits, self.group_size,
-                                  torch.float16, out=self._weight_scratch())
+            if route == "staged":
+                torch.cuda.current_stream(x2.device).wait_event(ready)
+                y = ops.dense_weight_gemm(x_hat, w16, bias, torch.float16)
+                self._stager.done(self)
+            elif route == "dense":
+                w16 = ops.unpack_weight_f16(self.packed_weight_codes, self.weight_center, self.weight_scale,
+                                            self.weight_code_sum, self.weight_codebook, self.bits, self.group_size,
+                                            out=self._weight_scratch())
                 y = ops.dense_weight_gemm(x_hat, w16, bias, torch.float16)
             else:
                 y = ops.packed_weight_gemm(x_hat, self.packed_weight_codes, self.weight_center, self.weight_scale,

@@ -1,0 +1,113 @@
+"""Weight staging for the on-the-fly linears: unpack layer L+1 while layer L computes.
+
+The reference's on-the-fly layer unpacks its weight into a shared fp16 scratch matrix and then calls a dense
+GEMM (fair_qat/arcq_packed_on_the_fly.py:147-160, scratch attached by
+scripts/benchmark_arcq_on_the_fly.py:189-191).  Here the same two steps run on two streams: the unpack of the
+next layer's weight goes to a side stream and into the other of two scratch matrices, so that by the time the
+next layer's activations are quantised its weight is already in L2 and the GEMM reads both operands by TMA.
+Nothing but the packed codes is kept between forwards; the scratch is two matrices of the largest layer.
+
+The order of the layers is their registration order in the model (timm's and this package's ViT register
+qkv, proj, fc1, fc2 block by block, which is the order they run in).  A layer that is called out of that
+order, or on its own, simply unpacks its weight when it is called.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import ops
+
+
+class WeightStager:
+    #: a GEMM with fewer rows than this keeps the packed-weight kernel (the unpack would not pay off)
+    min_rows = 1024
+
+    def __init__(self, model: nn.Module, layer_type: type):
+        self.layers: List[nn.Module] = [m for m in model.modules() if isinstance(m, layer_type)]
+        for i, m in enumerate(self.layers):
+            m._stager, m._stage_index = self, i
+        self._side: Optional[torch.cuda.Stream] = None
+        self._scratch: List[Optional[torch.Tensor]] = [None, None]
+        self._reset()
+        model.register_forward_pre_hook(self._begin)
+        model.register_forward_hook(self._end)
+
+    # ---- per-forward state: which layer each scratch matrix holds, and the events that order the two streams
+    def _reset(self) -> None:
+        self._holds: List[Optional[int]] = [None, None]
+        self._ready: List[Optional[torch.cuda.Event]] = [None, None]     # unpack into scratch b finished
+        self._free: List[Optional[torch.cuda.Event]] = [None, None]      # the GEMM that read scratch b finished
+
+    def _begin(self, module, args) -> None:
+        self._reset()
+
+    def _end(self, module, args, output) -> None:
+        if self._side is not None and any(h is not None for h in self._holds):
+            torch.cuda.current_stream().wait_stream(self._side)     # nothing of the side stream outlives the forward
+        self._reset()
+
+    def _buffer(self, b: int, layer: nn.Module) -> torch.Tensor:
+        need = max(m.in_features * m.out_features for m in self.layers)
+        buf = self._scratch[b]
+        dev = layer.packed_weight_codes.device
+        if buf is None or buf.numel() < need or buf.device != dev:
+            buf = torch.empty(need, dtype=torch.float16, device=dev)
+            self._scratch[b] = buf
+            self._holds[b] = None
+        return buf
+
+    def _unpack(self, i: int, cur: torch.cuda.Stream) -> None:
+        layer, b = self.layers[i], i & 1
+        buf = self._buffer(b, layer)
+        if self._side is None or self._side.device != buf.device:
+            self._side = torch.cuda.Stream(device=buf.device)
+        if self._free[b] is not None:
+            self._side.wait_event(self._free[b])          # the previous reader of this scratch matrix is done
+        else:
+            self._side.wait_stream(cur)                   # first use in this forward: order after everything so far
+        ops.unpack_weight_f16(layer.packed_weight_codes, layer.weight_center, layer.weight_scale, layer.weight_code_sum,
+                              layer.weight_codebook, layer.bits, layer.group_size, out=buf, stream=self._side)
+        ev = torch.cuda.Event()
+        ev.record(self._side)
+        self._ready[b], self._holds[b] = ev, i
+
+    def stage(self, layer: nn.Module) -> Tuple[torch.Tensor, torch.cuda.Event]:
+        """(fp16 weight [N, K] of ``layer``, event to wait for before reading it).  Also starts the unpack of
+        the layer registered after it.  Call before the layer's activation quantizer is launched."""
+        cur = torch.cuda.current_stream(layer.packed_weight_codes.device)
+        i = layer._stage_index
+        b = i & 1
+        if self._holds[b] != i:
+            self._unpack(i, cur)
+        if i + 1 < len(self.layers) and self._holds[(i + 1) & 1] != i + 1:
+            self._unpack(i + 1, cur)
+        w16 = self._scratch[b][: layer.out_features * layer.in_features].view(layer.out_features, layer.in_features)
+        return w16, self._ready[b]
+
+    def done(self, layer: nn.Module) -> None:
+        """Call after the GEMM that reads the layer's staged weight has been launched."""
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(layer.packed_weight_codes.device))
+        self._free[layer._stage_index & 1] = ev
+
+    def scratch_bytes(self) -> int:
+        return sum(b.numel() * 2 for b in self._scratch if b is not None)
+
+
+def attach_weight_stager(model: nn.Module) -> Optional[WeightStager]:
+    """Give the on-the-fly linears of ``model`` a common stager (idempotent); None if the model has none."""
+    from .packed_linear import ARCQPackedLinearOnTheFly
+    old = getattr(model, "_arcq_weight_stager", None)
+    layers = [m for m in model.modules() if isinstance(m, ARCQPackedLinearOnTheFly)]
+    if old is not None and old.layers == layers:
+        return old
+    if not layers:
+        return None
+    if old is not None:
+        raise RuntimeError("the model's packed layers changed after a weight stager was attached")
+    stager = WeightStager(model, ARCQPackedLinearOnTheFly)
+    object.__setattr__(model, "_arcq_weight_stager", stager)
+    return stager

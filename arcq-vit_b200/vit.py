@@ -20,6 +20,7 @@ import torch.nn.functional as F
 
 from . import codebook as cbk
 from .packed_linear import ARCQPackedLinear, ARCQPackedLinearOnTheFly
+from .staging import attach_weight_stager
 
 # name -> (embed dim, heads, depth); MLP hidden = 4 * dim; 224x224 input, patch 16, 1000 classes
 DEIT_CONFIGS: Dict[str, Tuple[int, int, int]] = {
@@ -214,6 +215,8 @@ def quantise_model(model: VisionTransformer, calib_images: torch.Tensor, bits: i
     model(calib_images)
     for n in names:
         _set(model, n, _get(model, n).packed)
+    if on_the_fly:
+        attach_weight_stager(model)
     return model
 
 
@@ -225,6 +228,8 @@ def pack_model_with_codebooks(model: VisionTransformer, codebooks: Dict[str, Dic
         c = codebooks[n]
         _set(model, n, pack_linear(_get(model, n), bits, c["act_cb"], c["act_th"], c["w_cb"], c["w_th"], group_size,
                                    on_the_fly))
+    if on_the_fly:
+        attach_weight_stager(model)
     return model
 
 

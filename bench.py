@@ -432,7 +432,23 @@ def run_gpu_arm(a):
     ms_e2e = f0.elapsed_time(f1)
     host_logits = pipe.out_host[0]
     clocks = sampler.stop() if rank == 0 else None
+    rank_ms = None
     if world > 1:
+        # the same steps without the gather, so that the per-rank spread (one GPU slower than another) can be told
+        # from what the collective costs
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync_all()
+        g0.record()
+        with torch.no_grad():
+            for i in range(a.steps):
+                runner(dev_batches[i % n_rot])
+        g1.record()
+        sync_all()
+        mine = torch.tensor([ms, g0.elapsed_time(g1)], device=dev, dtype=torch.float64) / a.steps
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        rank_ms = {"with_gather": [round(float(v[0]), 4) for v in every],
+                   "forward_only": [round(float(v[1]), 4) for v in every]}
         t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(t[0]), float(t[1])
@@ -490,6 +506,7 @@ def run_gpu_arm(a):
         }
         if gather_check is not None:
             line["gather_check"] = gather_check
+            line["rank_ms_per_step"] = rank_ms
         line.update(extra)
         if cpu is not None:
             line["cpu_baseline"] = cpu

@@ -204,6 +204,18 @@ int arcq_add_layernorm(const void* x, const void* y, const float* gamma, const f
                        int64_t M, int64_t K, void* sum_out, void* h_out, void* stream);
 
 /*
+ * arcq_add_layernorm followed by the activation quantizer of the packed linear that consumes the LayerNorm
+ * output (timm Block.forward: norm1 -> attn.qkv, norm2 -> mlp.fc1), in one kernel:
+ *   s = fp16(x + y) -> sum_out (y and sum_out may be NULL together);  h = fp16(LayerNorm(s));
+ *   xhat = what arcq_act_quant(h, ..., xhat_dtype fp16) reconstructs.
+ * h is not written unless h_out is given (for checking: arcq_act_quant on that h gives the same xhat bits).
+ * fp16 rows of K values, K a multiple of 64 and at most 1024; group_size 64.
+ */
+int arcq_add_layernorm_act_quant(const void* x, const void* y, const float* gamma, const float* beta, float eps,
+                                 int64_t M, int64_t K, const float* thresholds, const float* codebook, int bits,
+                                 int group_size, void* sum_out, void* h_out, void* xhat, void* stream);
+
+/*
  * Unpack codes to one byte per code.  Replaces unpack_codes_u8_cuda,
  * EXT/arcq_pack_kernel.cu:136-157 (kernel :74-90); the int64 variant
  * unpack_codes_cuda (:113-134) is this plus a widening on the host side.
@@ -228,6 +240,18 @@ int arcq_pack_codes(const uint8_t* codes, int64_t rows, int64_t length, int bits
 int arcq_dequant(const uint8_t* packed, const float* mu, const float* sigma, const float* codesum,
                  const float* codebook, int bits, int group_size, int64_t rows, int64_t K,
                  void* out, int out_dtype, void* stream);
+
+/*
+ * The fp16 weight exactly as arcq_packed_weight_gemm rebuilds it on chip:
+ * out = fp16(mu - sigma*codesum/64) + fp16(sigma) * fp16(cb[c]) in one half-precision fused multiply-add.
+ * Written into a scratch matrix [rows, K] and read by arcq_dense_weight_gemm, the pair gives the same bits
+ * as arcq_packed_weight_gemm.  This is the reference's own data flow (unpack_weight_triton into
+ * `_weight_buffer`, then F.linear: FQ/fair_qat/arcq_packed_on_the_fly.py:147-160); the unpack of layer
+ * L+1 can run on a second stream while layer L computes.  group_size 64 only.
+ */
+int arcq_unpack_weight_f16(const uint8_t* packed, const float* mu, const float* sigma, const float* codesum,
+                           const float* codebook, int bits, int group_size, int64_t rows, int64_t K,
+                           void* out, void* stream);
 
 #ifdef __cplusplus
 }

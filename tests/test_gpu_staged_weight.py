@@ -1,0 +1,117 @@
+"""The reference's data flow on two streams: the weight is unpacked into an fp16 scratch matrix
+(``arcq_unpack_weight_f16``) and read by the dense-weight GEMM on CTA pairs, the unpack of the next layer
+running beside the current layer.  Checked here: the unpacked matrix holds exactly the bits the packed-weight
+kernels rebuild on chip, the pair form of the dense GEMM equals the one-CTA form, and a whole model gives the
+same logits whichever way its weights reach the tensor cores, eagerly and from a CUDA graph."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _weight(pkg, dev, K, N, bits, seed):
+    gen = torch.Generator().manual_seed(seed)
+    cb = torch.sort(torch.randn(2 ** bits, generator=gen) * 1.2)[0].to(dev)
+    th = (cb[:-1] + cb[1:]) / 2
+    w = (torch.randn(N, K, generator=gen) * 0.02).to(dev)
+    bias = (torch.randn(N, generator=gen) * 0.01).to(dev)
+    pw, mw, sw, cw = pkg.ops.quantize_activation(w, th, cb, bits, 64)
+    return pw, mw, sw, cw, cb, bias
+
+
+@pytest.mark.parametrize("bits", [4, 3, 2])
+@pytest.mark.parametrize("M,K,N", [(300, 384, 192), (64 * 197, 384, 1152), (2049, 1536, 384), (1500, 768, 2304)])
+def test_unpacked_weight_and_dense_gemm_equal_the_packed_weight_gemm(pkg, oracle, cuda_device, M, K, N, bits):
+    if not pkg.ops.packed_weight_gemm_supported(K, N, bits, 64):
+        pytest.skip("shape is routed to the packed-codes kernel")
+    pw, mw, sw, cw, cb, bias = _weight(pkg, cuda_device, K, N, bits, seed=K + N + bits)
+    xh = torch.randn(M, K, generator=torch.Generator().manual_seed(M)).half().to(cuda_device)
+    scratch = torch.full((N * K + 64,), float("nan"), dtype=torch.float16, device=cuda_device)
+    w16 = pkg.ops.unpack_weight_f16(pw, mw, sw, cw, cb, bits, 64, out=scratch)
+    assert w16.data_ptr() == scratch.data_ptr() and tuple(w16.shape) == (N, K)
+    assert bool(torch.isnan(scratch[N * K:]).all()), "wrote past the matrix"
+    # close to the fp32 reconstruction (it differs by the fp16 rounding of the folded statistics only)
+    w32 = pkg.ops.dequant(pw, mw, sw, cw, cb, bits, 64, torch.float32)
+    assert float((w16.float() - w32).abs().max()) < 4e-3 * float(w32.abs().max())
+    for out_dtype in (torch.float16, torch.float32):
+        with pkg._cabi.option("ARCQ_PAIR_MIN_M", 1):
+            y_dense = pkg.ops.dense_weight_gemm(xh, w16, bias, out_dtype)
+            y_packed = pkg.ops.packed_weight_gemm(xh, pw, mw, sw, cw, cb, bias, bits, 64, out_dtype)
+        assert torch.equal(y_dense, y_packed)
+    assert pkg.ops.device_status() == 0
+
+
+@pytest.mark.parametrize("options", [dict(), dict(ARCQ_PAIR_BN=32), dict(ARCQ_PAIR_BN=64), dict(ARCQ_PAIR_BN=96),
+                                     dict(ARCQ_PAIR_BN=128), dict(ARCQ_PAIR_BN=192), dict(ARCQ_PAIR_BN=256),
+                                     dict(ARCQ_PAIR_KS=1), dict(ARCQ_PAIR_KS=3), dict(ARCQ_PAIR_SA=2),
+                                     dict(ARCQ_PAIR_BN=192, ARCQ_PAIR_KS=1, ARCQ_PAIR_SA=5), dict(ARCQ_PAIR_PAIRS=7)])
+@pytest.mark.parametrize("M,K,N", [(256, 64, 768), (2500, 384, 768), (64 * 197, 384, 1536), (5000, 1536, 768)])
+def test_dense_pair_kernel_equals_the_one_cta_kernel(pkg, cuda_device, M, K, N, options):
+    gen = torch.Generator().manual_seed(M + K + N)
+    x = torch.randn(M, K, generator=gen).half().to(cuda_device)
+    w = (torch.randn(N, K, generator=gen) * 0.05).half().to(cuda_device)
+    b = torch.randn(N, generator=gen).to(cuda_device)
+    for out_dtype in (torch.float16, torch.float32):
+        with pkg._cabi.option("ARCQ_PAIR", 0):
+            y_one = pkg.ops.dense_weight_gemm(x, w, b, out_dtype)
+        saved = {k: pkg._cabi.get_option(k) for k in options}
+        try:
+            for k, v in options.items():
+                pkg._cabi.set_option(k, v)
+            with pkg._cabi.option("ARCQ_PAIR_MIN_M", 1):
+                y_pair = pkg.ops.dense_weight_gemm(x, w, b, out_dtype)
+        finally:
+            for k, v in saved.items():
+                pkg._cabi.set_option(k, v)
+        assert pkg.ops.device_status() == 0, f"a bounded wait ran out with {options}"
+        assert torch.equal(y_pair, y_one), options
+    # rows do not depend on the batch they are computed in
+    with pkg._cabi.option("ARCQ_PAIR_MIN_M", 1):
+        y_all = pkg.ops.dense_weight_gemm(x, w, b, torch.float16)
+        y_part = pkg.ops.dense_weight_gemm(x[: min(M, 131)].contiguous(), w, b, torch.float16)
+    assert torch.equal(y_all[: y_part.shape[0]], y_part)
+
+
+@pytest.mark.parametrize("bits", [4, 3])
+def test_whole_model_logits_do_not_depend_on_the_weight_route(pkg, cuda_device, bits):
+    """DeiT-T at batch 8 (1576 rows: above the stager's row threshold): packed, dense on one stream, and staged on
+    two streams give the same logits, eagerly and replayed from a CUDA graph; the stager's scratch is two
+    matrices of the largest layer."""
+    dev = cuda_device
+    gen = torch.Generator().manual_seed(5)
+    model = pkg.create_vit("deit_tiny", seed=1).half().to(dev)
+    x = torch.randn(8, 3, 224, 224, generator=gen).half().to(dev)
+    x2 = torch.randn(8, 3, 224, 224, generator=gen).half().to(dev)
+    cls = pkg.ARCQPackedLinearOnTheFly
+    saved = cls.weight_form
+    try:
+        with torch.no_grad():
+            model = pkg.quantise_model(model, x, bits)
+            stager = model._arcq_weight_stager
+            assert len(stager.layers) == 48 and all(m._stager is stager for m in stager.layers)
+            assert pkg.attach_weight_stager(model) is stager            # idempotent
+            want = {}
+            for form in ("packed", "dense", "staged", "auto"):
+                cls.weight_form = form
+                y = model(x).clone()
+                y2 = model(x2).clone()
+                runner = pkg.GraphedModel(model, x)
+                g = runner(x).clone()
+                g2 = runner(x2).clone()
+                torch.cuda.synchronize()
+                assert pkg.ops.device_status() == 0
+                assert torch.equal(y, g) and torch.equal(y2, g2), form
+                if form == "packed":
+                    want = {"y": y, "y2": y2}
+                assert torch.equal(y, want["y"]) and torch.equal(y2, want["y2"]), form
+            assert stager.scratch_bytes() == 2 * 2 * 768 * 192
+            # a layer called on its own, outside the model's forward, unpacks its weight when it is called
+            cls.weight_form = "staged"
+            layer = stager.layers[5]
+            h = torch.randn(1500, layer.in_features, generator=gen).half().to(dev)
+            y_alone = layer(h)
+            cls.weight_form = "packed"
+            assert torch.equal(y_alone, layer(h))
+    finally:
+        cls.weight_form = saved
