@@ -534,7 +534,7 @@ bool choose_pair_config(long long M, long long N, long long K, int bits, bool y_
 
 // ---- dense-weight CTA-pair kernel: configuration ----
 struct PairDenseConfig {
-  int bn, sa, ks, pairs;
+  int bn, sa, ks, pairs, stationary;
   size_t smem;
 };
 
@@ -553,7 +553,7 @@ int max_resident_dense_pairs(size_t smem) {
   attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, arcq::dense_weight_gemm_pair_kernel, &cfg);
+  const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, arcq::dense_weight_gemm_pair_kernel<true>, &cfg);
   if (e != cudaSuccess || n <= 0) {
     cudaGetLastError();
     n = sm_count() / 2;
@@ -578,7 +578,9 @@ bool choose_pair_dense_config(long long M, long long N, long long K, bool y_f32,
     int dev = 0;
     cudaGetDevice(&dev);
     if (done_dev != dev) {
-      if (cudaFuncSetAttribute(arcq::dense_weight_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      if (cudaFuncSetAttribute(arcq::dense_weight_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(full_smem)) != cudaSuccess ||
+          cudaFuncSetAttribute(arcq::dense_weight_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(full_smem)) != cudaSuccess) {
         cudaGetLastError();
         return false;
@@ -600,25 +602,37 @@ bool choose_pair_dense_config(long long M, long long N, long long K, bool y_f32,
     long long per = max_pairs / slabs;
     if (per > tiles_m) per = tiles_m;
     const long long tiles_pp = (tiles_m + per - 1) / per;
-    PairDenseConfig k = {};
-    k.bn = bn; k.pairs = static_cast<int>(slabs * per);
-    k.ks = (G % 2 == 0) ? 2 : (G % 3 == 0) ? 3 : 1;
-    if (opt(O_PAIR_KS) > 0 && G % opt(O_PAIR_KS) == 0) k.ks = opt(O_PAIR_KS);
-    bool fits = false;
-    for (int sa = 16; sa >= 2 && !fits; --sa) {
-      if (opt(O_PAIR_SA) > 0 && sa != opt(O_PAIR_SA)) continue;
-      if (sa * k.ks > 8 && opt(O_PAIR_SA) == 0) continue;             // eight sub-stages in flight are plenty
-      const size_t need = arcq::pair_dense_smem_layout(bn, sa, k.ks).total;
-      if (need <= kSmemBudget) { k.sa = sa; k.smem = need + 1024; fits = true; }
-    }
-    if (!fits) continue;
     const int esize = y_f32 ? 4 : 2;
     const double t_write = 128.0 * bn * esize / 22.0e3;
-    const double t_issue = (G / k.ks) * (k.ks * 4 * (bn > 128 ? 0.056 * bn / 192.0 : 0.04) + 0.1);
-    const double t_l2 = static_cast<double>(slabs) * M * K * 2.0 / 5.0e6;
-    const double path = tiles_pp * ((t_write > t_issue ? t_write : t_issue) + 0.15);
-    const double cost = 1.5 + (path > t_l2 ? path : t_l2);
-    if (!found || cost < best_cost) { best = k; best_cost = cost; found = true; }
+    for (int stationary = 1; stationary >= 0; --stationary) {
+      if (opt(O_PAIR_STATIONARY) >= 0 && stationary != opt(O_PAIR_STATIONARY)) continue;
+      if (stationary && G > 32) continue;
+      PairDenseConfig k = {};
+      k.bn = bn; k.pairs = static_cast<int>(slabs * per); k.stationary = stationary;
+      k.ks = (G % 2 == 0) ? 2 : (G % 3 == 0) ? 3 : 1;
+      if (opt(O_PAIR_KS) > 0 && G % opt(O_PAIR_KS) == 0) k.ks = opt(O_PAIR_KS);
+      bool fits = false;
+      for (int sa = 16; sa >= 2 && !fits; --sa) {
+        if (opt(O_PAIR_SA) > 0 && sa != opt(O_PAIR_SA)) continue;
+        if (sa * k.ks > 8 && opt(O_PAIR_SA) == 0) continue;             // eight sub-stages in flight are plenty
+        const size_t need = arcq::pair_dense_smem_layout(bn, sa, k.ks, G, stationary != 0).total;
+        if (need <= kSmemBudget) { k.sa = sa; k.smem = need + 1024; fits = true; }
+      }
+      if (!fits) continue;
+      if (stationary && opt(O_PAIR_STATIONARY) < 0 && (k.sa * k.ks < 4 || tiles_pp < 3))
+        continue;   // too little room left for A, or too few tiles to pay for loading the whole slab first
+      const double t_issue = (G / k.ks) * (k.ks * 4 * (bn > 128 ? 0.056 * bn / 192.0 : 0.04) + 0.1);
+      // shared-memory fill through L2, about 8 TB/s over the machine: every tile streams its A rows, and its
+      // W16 rows too unless the slab is stationary
+      const double fill_mb = (static_cast<double>(slabs) * M * K * 2.0 +
+                              (stationary ? static_cast<double>(k.pairs) : static_cast<double>(slabs * tiles_m)) * bn * K * 2.0) / 1.0e6;
+      const double t_fill = fill_mb / 8.0;
+      // 0.45 us per tile that neither the stores nor the issue account for (measured: at equal store volume, 192-wide
+      // slabs beat 128-wide ones on N = 1152 by 1 us over 5 against 7 tiles per pair)
+      const double path = tiles_pp * ((t_write > t_issue ? t_write : t_issue) + 0.45) * (stationary ? 0.95 : 1.0);
+      const double cost = 1.5 + (path > t_fill ? path : t_fill);
+      if (!found || cost < best_cost) { best = k; best_cost = cost; found = true; }
+    }
   }
   if (!found) return false;
   *c = best;
@@ -920,8 +934,12 @@ static int launch_pair_dense_gemm(const PairDenseConfig& cfg, const void* xhat, 
   p.spin_limit = static_cast<uint32_t>(opt(O_SPIN_LIMIT));
   p.status = status_ptr();
   if (p.status == nullptr) return fail(ARCQ_E_CUDA, "device status word not reachable");
-  launch_pdl(arcq::dense_weight_gemm_pair_kernel, static_cast<unsigned>(2 * cfg.pairs), arcq::kPairDenseThreads, cfg.smem,
-             static_cast<cudaStream_t>(stream), tm_a, tm_w, tm_y, p);
+  if (cfg.stationary)
+    launch_pdl(arcq::dense_weight_gemm_pair_kernel<true>, static_cast<unsigned>(2 * cfg.pairs), arcq::kPairDenseThreads,
+               cfg.smem, static_cast<cudaStream_t>(stream), tm_a, tm_w, tm_y, p);
+  else
+    launch_pdl(arcq::dense_weight_gemm_pair_kernel<false>, static_cast<unsigned>(2 * cfg.pairs), arcq::kPairDenseThreads,
+               cfg.smem, static_cast<cudaStream_t>(stream), tm_a, tm_w, tm_y, p);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "dense_weight_gemm (pair) launch");
   return ARCQ_OK;

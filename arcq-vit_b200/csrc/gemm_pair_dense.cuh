@@ -12,6 +12,11 @@
 //   warps 2-9   epilogue: tensor memory -> registers -> + bias -> fp16/fp32 -> staging -> TMA store
 // and the kernel starts issuing as soon as its first stage has landed (no table or statistics set-up).
 //
+// STATIONARY: the pair's whole W16 slab (bn/2 rows x K per CTA) is loaded once and stays in shared memory for
+// all the row tiles the pair works on; only A streams through the stages.  With K = 384 the operands of a
+// 256 x 192 tile are used for so few flops that the L2 -> shared-memory traffic (about 8 TB/s over all SMs)
+// bounds the kernel, and the slab is 43 % of that traffic.
+//
 // Each output element is the fp32 sum over k in ascending order of 16-wide steps, as in every other GEMM
 // kernel of this library.
 #pragma once
@@ -37,33 +42,40 @@ struct PairDenseParams {
 constexpr int kPairDenseThreads = (2 + kPairEpiWarps) * 32;
 
 struct PairDenseSmem {
-  uint32_t stages, stage, misc, total;
+  uint32_t stages, slab, stage, misc, total;
 };
-__host__ __device__ inline PairDenseSmem pair_dense_smem_layout(int bn, int sa, int ks) {
+constexpr int kPairDenseBarriers = 72;
+__host__ __device__ inline PairDenseSmem pair_dense_smem_layout(int bn, int sa, int ks, int G, bool stationary) {
   PairDenseSmem s;
-  const uint32_t stage_bytes = static_cast<uint32_t>(ks) * (kStageA + static_cast<uint32_t>(bn / 2) * 128u);
+  const uint32_t wtile = static_cast<uint32_t>(bn / 2) * 128u;
+  const uint32_t stage_bytes = static_cast<uint32_t>(ks) * (kStageA + (stationary ? 0u : wtile));
   s.stages = 0;
-  s.stage = static_cast<uint32_t>(sa) * stage_bytes;
+  s.slab = static_cast<uint32_t>(sa) * stage_bytes;
+  s.stage = s.slab + (stationary ? static_cast<uint32_t>(G) * wtile : 0u);
   s.misc = s.stage + kPairEpiStageBytes;
-  s.total = s.misc + 256 * 4 /*bias*/ + 40 * 8 /*barriers*/ + 16 /*tensor-memory address*/;
+  s.total = s.misc + 256 * 4 /*bias*/ + kPairDenseBarriers * 8 + 16 /*tensor-memory address*/;
   return s;
 }
 
+template <bool STATIONARY>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairDenseThreads, 1)
     dense_weight_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                                   const __grid_constant__ CUtensorMap tm_y, const PairDenseParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* const smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  const PairDenseSmem L = pair_dense_smem_layout(p.bn, p.sa, p.ks);
+  const PairDenseSmem L = pair_dense_smem_layout(p.bn, p.sa, p.ks, p.G, STATIONARY);
   uint8_t* const sStages = smem + L.stages;
+  uint8_t* const sSlab = smem + L.slab;
   uint8_t* const sStage = smem + L.stage;
   float* const s_bias = reinterpret_cast<float*>(smem + L.misc);
   uint64_t* const bars = reinterpret_cast<uint64_t*>(s_bias + 256);
   // barriers: full [sa] <= 16 at 0 (leader: both CTAs' bytes of the stage landed);  empty [sa] at 16 (both: the
-  // MMAs that read the stage are done);  acc_full [2] at 32 (both);  acc_empty [2] at 34 (leader)
+  // MMAs that read the stage are done);  acc_full [2] at 32 (both);  acc_empty [2] at 34 (leader);
+  // slab_full [G] <= 32 at 40 (leader, stationary slab only: sub-tile g of both CTAs landed)
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t full = bar0, empty = bar0 + 16 * 8, acc_full = bar0 + 32 * 8, acc_empty = bar0 + 34 * 8;
-  uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(bars + 40);
+  const uint32_t slab_full = bar0 + 40 * 8;
+  uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(bars + kPairDenseBarriers);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t crank = cluster_ctarank();     // 0: leader
@@ -87,12 +99,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairDenseThreads, 1
   };
   const uint32_t poll_limit = p.poll_limit, spin_limit = p.spin_limit;
   const uint32_t wtile_bytes = static_cast<uint32_t>(hb) * 128u;
-  const uint32_t stage_bytes = static_cast<uint32_t>(ks) * (kStageA + wtile_bytes);
+  const uint32_t stage_bytes = static_cast<uint32_t>(ks) * (kStageA + (STATIONARY ? 0u : wtile_bytes));
 
   pdl_launch_dependents();
   if (tid == 0) {
     for (int i = 0; i < p.sa; ++i) { mbar_init(&bars[i], 1); mbar_init(&bars[16 + i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&bars[32 + i], 1); mbar_init(&bars[34 + i], 2 * kPairEpiWarps); }
+    if (STATIONARY)
+      for (int i = 0; i < p.G; ++i) mbar_init(&bars[40 + i], 1);
     mbar_fence_init();
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_w);
@@ -117,6 +131,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairDenseThreads, 1
     uint32_t good = 1;
     // Both operands are other kernels' outputs (the activation quantizer's and the weight unpack's).
     pdl_wait();
+    if (STATIONARY && my_tiles > 0) {
+      // the whole slab, once; its sub-tiles land while the first A stages do
+      if (elect_one()) {
+        const uint32_t slab_leader = mapa_shared(slab_full, 0);
+        const uint32_t sl0 = smem_u32(sSlab);
+        for (int g = 0; g < G; ++g) {
+          if (crank == 0) mbar_expect_tx(slab_full + g * 8, 2u * wtile_bytes);
+          tma_load_2d_pair(sl0 + g * wtile_bytes, &tm_w, slab_leader + g * 8, g * 64, nh0);
+        }
+      }
+      __syncwarp();
+    }
     for (int t = 0; t < my_tiles; ++t) {
       const int row0 = row_of(t);
       for (int g0 = 0; g0 < G; g0 += ks) {
@@ -127,8 +153,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairDenseThreads, 1
             const uint32_t dst = st0 + slot * stage_bytes;
             for (int q = 0; q < ks; ++q)
               tma_load_2d_pair(dst + q * kStageA, &tm_a, full_leader + slot * 8, (g0 + q) * 64, row0);
-            for (int q = 0; q < ks; ++q)
-              tma_load_2d_pair(dst + ks * kStageA + q * wtile_bytes, &tm_w, full_leader + slot * 8, (g0 + q) * 64, nh0);
+            if (!STATIONARY)
+              for (int q = 0; q < ks; ++q)
+                tma_load_2d_pair(dst + ks * kStageA + q * wtile_bytes, &tm_w, full_leader + slot * 8, (g0 + q) * 64, nh0);
           }
         }
         __syncwarp();
@@ -149,6 +176,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairDenseThreads, 1
       const uint32_t sa = p.sa;
       const uint32_t lo0 = ((smem_u32(sStages) & 0x3FFFFu) >> 4) | (1u << 16);
       const uint32_t s_step = stage_bytes >> 4, w_off = (static_cast<uint32_t>(ks) * kStageA) >> 4, w_step = wtile_bytes >> 4;
+      const uint32_t slab_lo0 = ((smem_u32(sSlab) & 0x3FFFFu) >> 4) | (1u << 16);
       const uint32_t empty_r = mapa_shared(empty, 1), acc_full_r = mapa_shared(acc_full, 1);
       uint32_t slot = 0, ph = 0, lo = lo0;
       uint32_t acc_ph0 = 1, acc_ph1 = 1;   // acc_empty phases: the first use of each buffer is free
@@ -162,11 +190,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairDenseThreads, 1
         const uint32_t d = tmem_base + buf * 256;
         uint32_t acc = 0;
         for (int g0 = 0; g0 < G; g0 += ks) {
+          if (STATIONARY && t == 0) {   // the slab lands while the first tile runs
+            for (int q = 0; q < ks; ++q) good &= mbar_spin_flag(slab_full + (g0 + q) * 8, 0u, good ? spin_limit : 0u);
+          }
           good &= mbar_spin_flag(full + slot * 8, ph, good ? spin_limit : 0u);
           tc_fence_after_sync();
           if (elect_one()) {
             if (good) {
-              uint32_t al = lo, wl = lo + w_off;
+              uint32_t al = lo, wl = STATIONARY ? slab_lo0 + static_cast<uint32_t>(g0) * w_step : lo + w_off;
               for (int q = 0; q < ks; ++q) {
                 umma_pair_f16_x4(d, al, wl, idesc, (q == 0) ? acc : 1u);
                 al += kStageA >> 4;

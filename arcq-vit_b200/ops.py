@@ -183,14 +183,7 @@ def add_layernorm(x: torch.Tensor, y, norm: torch.nn.LayerNorm):
     K = shape[-1]
     x2 = _dev(x.reshape(-1, K), "x", torch.float16)
     y2 = None if y is None else _dev(y.reshape(-1, K), "y", torch.float16)
-    # fp32 copies of the affine parameters, remade whenever the parameters were replaced, written to or moved
-    key = (norm.weight.data_ptr(), norm.weight._version, norm.bias.data_ptr(), norm.bias._version, x2.device)
-    cached = getattr(norm, "_arcq_f32", None)
-    if cached is None or cached[0] != key:
-        cached = (key, norm.weight.detach().to(device=x2.device, dtype=torch.float32).contiguous(),
-                  norm.bias.detach().to(device=x2.device, dtype=torch.float32).contiguous())
-        norm._arcq_f32 = cached
-    _, g32, b32 = cached
+    g32, b32 = _norm_params_f32(norm, x2.device)
     h = torch.empty_like(x2)
     s_out = torch.empty_like(x2) if y2 is not None else None
     if x2.shape[0] > 0:
@@ -199,6 +192,44 @@ def add_layernorm(x: torch.Tensor, y, norm: torch.nn.LayerNorm):
                                     s_out.data_ptr() if s_out is not None else None, h.data_ptr(), _stream())
         _check(rc, "arcq_add_layernorm")
     return (x if s_out is None else s_out.reshape(shape)), h.reshape(shape)
+
+
+def _norm_params_f32(norm: torch.nn.LayerNorm, device):
+    """fp32 copies of the affine parameters, remade whenever the parameters were replaced, written to or moved."""
+    key = (norm.weight.data_ptr(), norm.weight._version, norm.bias.data_ptr(), norm.bias._version, device)
+    cached = getattr(norm, "_arcq_f32", None)
+    if cached is None or cached[0] != key:
+        cached = (key, norm.weight.detach().to(device=device, dtype=torch.float32).contiguous(),
+                  norm.bias.detach().to(device=device, dtype=torch.float32).contiguous())
+        norm._arcq_f32 = cached
+    return cached[1], cached[2]
+
+
+def add_layernorm_quant(x: torch.Tensor, y, norm: torch.nn.LayerNorm, thresholds: torch.Tensor, codebook: torch.Tensor,
+                        bits: int, group_size: int = 64, want_h: bool = False):
+    """``add_layernorm`` and the activation quantizer of the linear that consumes the LayerNorm output, in one
+    kernel: returns (x + y, xhat) where xhat is what ``quantize_activation_dequant(LayerNorm(x + y), ...)`` gives
+    in fp16; the LayerNorm output itself is not written.  ``want_h=True`` also returns it (third value), for
+    checking."""
+    lib = _cabi.load()
+    shape = x.shape
+    K = shape[-1]
+    x2 = _dev(x.reshape(-1, K), "x", torch.float16)
+    y2 = None if y is None else _dev(y.reshape(-1, K), "y", torch.float16)
+    thresholds, codebook = _dev(thresholds, "thresholds", torch.float32), _dev(codebook, "codebook", torch.float32)
+    g32, b32 = _norm_params_f32(norm, x2.device)
+    xhat = torch.empty_like(x2)
+    s_out = torch.empty_like(x2) if y2 is not None else None
+    h = torch.empty_like(x2) if want_h else None
+    if x2.shape[0] > 0:
+        rc = lib.arcq_add_layernorm_act_quant(x2.data_ptr(), y2.data_ptr() if y2 is not None else None, g32.data_ptr(),
+                                              b32.data_ptr(), float(norm.eps), x2.shape[0], K, thresholds.data_ptr(),
+                                              codebook.data_ptr(), bits, group_size,
+                                              s_out.data_ptr() if s_out is not None else None,
+                                              h.data_ptr() if h is not None else None, xhat.data_ptr(), _stream())
+        _check(rc, "arcq_add_layernorm_act_quant")
+    out = ((x if s_out is None else s_out.reshape(shape)), xhat.reshape(shape))
+    return out + (h.reshape(shape),) if want_h else out
 
 
 def unpack_codes_u8(packed: torch.Tensor, bits: int, length: int) -> torch.Tensor:

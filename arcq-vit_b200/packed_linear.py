@@ -296,9 +296,20 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
             return "dense"
         return form
 
-    def forward(self, x: torch.Tensor, pre_gelu: bool = False) -> torch.Tensor:
+    def takes_reconstructed_input(self) -> bool:
+        """True if ``forward(x_hat, pre_quantized=True)`` is available: the layer runs the two-kernel route whose
+        GEMM reads the reconstructed activation, so a caller may produce that activation itself
+        (``ops.add_layernorm_quant`` with this layer's ``activation_thresholds`` / ``activation_codebook``)."""
+        return (self.group_size == 64 and self.in_features <= 1024
+                and ops.packed_weight_gemm_supported(self.in_features, self.out_features, self.bits, self.group_size))
+
+    def forward(self, x: torch.Tensor, pre_gelu: bool = False, pre_quantized: bool = False) -> torch.Tensor:
         """``pre_gelu=True``: x is the pre-activation of the GELU in front of this layer; the result
-        equals ``forward(F.gelu(x))`` with the GELU fused into the activation quantizer."""
+        equals ``forward(F.gelu(x))`` with the GELU fused into the activation quantizer.
+        ``pre_quantized=True``: x is already this layer's reconstructed activation (see
+        ``takes_reconstructed_input``); the quantizer is skipped."""
+        if pre_quantized and (pre_gelu or not self.takes_reconstructed_input()):
+            raise ValueError("pre_quantized input is not available for this layer / combination")
         shape = x.shape
         if shape[-1] != self.in_features:
             raise ValueError(f"expected last dim {self.in_features}, got {shape[-1]}")
@@ -310,8 +321,8 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
             route = self._weight_route(x2.shape[0])
             if route == "staged":
                 w16, ready = self._stager.stage(self)     # starts the next layer's unpack on the side stream too
-            x_hat = ops.quantize_activation_dequant(x2, self.activation_thresholds, self.activation_codebook,
-                                                    self.bits, self.group_size, torch.float16, pre_gelu)
+            x_hat = x2 if pre_quantized else ops.quantize_activation_dequant(
+                x2, self.activation_thresholds, self.activation_codebook, self.bits, self.group_size, torch.float16, pre_gelu)
             if route == "staged":
                 torch.cuda.current_stream(x2.device).wait_event(ready)
                 y = ops.dense_weight_gemm(x_hat, w16, bias, torch.float16)

@@ -12,6 +12,7 @@ floating point (ordinary PyTorch ops).
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, Dict, List, Tuple
 
 import torch
@@ -37,9 +38,10 @@ class Attention(nn.Module):
         self.qkv = nn.Linear(dim, 3 * dim)
         self.proj = nn.Linear(dim, dim)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, pre_quantized: bool = False) -> torch.Tensor:
         B, T, C = x.shape
-        qkv = self.qkv(x).reshape(B, T, 3, self.num_heads, C // self.num_heads).permute(2, 0, 3, 1, 4)
+        qkv = self.qkv(x, pre_quantized=True) if pre_quantized else self.qkv(x)
+        qkv = qkv.reshape(B, T, 3, self.num_heads, C // self.num_heads).permute(2, 0, 3, 1, 4)
         o = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2])
         return self.proj(o.transpose(1, 2).reshape(B, T, C))
 
@@ -50,8 +52,8 @@ class Mlp(nn.Module):
         self.fc1 = nn.Linear(dim, hidden)
         self.fc2 = nn.Linear(hidden, dim)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        h = self.fc1(x)
+    def forward(self, x: torch.Tensor, pre_quantized: bool = False) -> torch.Tensor:
+        h = self.fc1(x, pre_quantized=True) if pre_quantized else self.fc1(x)
         if getattr(self.fc2, "supports_pre_gelu", False) and h.dtype == torch.float16:
             return self.fc2(h, pre_gelu=True)       # GELU fused into fc2's activation quantizer
         return self.fc2(F.gelu(h))
@@ -86,6 +88,13 @@ class PatchEmbed(nn.Module):
 
 
 class VisionTransformer(nn.Module):
+    # The LayerNorm in front of qkv / fc1 can also run that layer's activation quantizer (one kernel instead of
+    # two, the LayerNorm output never written).  Off by default: both kernels are bound by instruction issue, not
+    # by memory, so the merged kernel costs the sum of the two (16.1 us against 17.8 us for [12608, 384]) and the
+    # whole DeiT-S forward measured 4 % slower with it, because two short kernels overlap better with their
+    # neighbours than one long one.
+    fuse_norm_quant = os.environ.get("ARCQ_LN_QUANT", "0") != "0"
+
     def __init__(self, dim: int, heads: int, depth: int, num_classes: int = 1000, img_size: int = 224,
                  patch: int = 16):
         super().__init__()
@@ -111,13 +120,27 @@ class VisionTransformer(nn.Module):
         """Same computation as the loop over blocks, with every residual add merged into the LayerNorm
         that follows it (one kernel instead of two): x += attn(norm1(x)); x += mlp(norm2(x))."""
         from . import ops
-        _, h = ops.add_layernorm(x, None, self.blocks[0].norm1)
+
+        def norm_into(x, y, norm, lin):
+            """(x + y, input of `lin`, whether that input is already quantised): the LayerNorm in front of a packed
+            linear also runs that linear's activation quantizer when the layer can take the result."""
+            if self.fuse_norm_quant and isinstance(lin, ARCQPackedLinearOnTheFly) and lin.takes_reconstructed_input():
+                s, xh = ops.add_layernorm_quant(x, y, norm, lin.activation_thresholds, lin.activation_codebook,
+                                                lin.bits, lin.group_size)
+                return s, xh, True
+            s, h = ops.add_layernorm(x, y, norm)
+            return s, h, False
+
         n = len(self.blocks)
+        _, h, q = norm_into(x, None, self.blocks[0].norm1, self.blocks[0].attn.qkv)
         for i, blk in enumerate(self.blocks):
-            a = blk.attn(h)
-            x, h = ops.add_layernorm(x, a, blk.norm2)
-            m = blk.mlp(h)
-            x, h = ops.add_layernorm(x, m, self.blocks[i + 1].norm1 if i + 1 < n else self.norm)
+            a = blk.attn(h, pre_quantized=True) if q else blk.attn(h)
+            x, h, q = norm_into(x, a, blk.norm2, blk.mlp.fc1)
+            m = blk.mlp(h, pre_quantized=True) if q else blk.mlp(h)
+            if i + 1 < n:
+                x, h, q = norm_into(x, m, self.blocks[i + 1].norm1, self.blocks[i + 1].attn.qkv)
+            else:
+                x, h = ops.add_layernorm(x, m, self.norm)
         return self.head(h[:, 0])
 
 

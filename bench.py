@@ -204,7 +204,7 @@ def kernel_rooflines(pkg, a, dev, pk):
     reps, rot = a.reps, 4
     out = {}
     wanted = a.layers.split(",")
-    tot_flop = tot_ms = tot_bytes = aq_bytes = aq_ms = 0.0
+    tot_flop = tot_ms = tot_bytes = aq_bytes = aq_ms = aq_copy_ms = 0.0
     per_layer = []
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
@@ -239,39 +239,63 @@ def kernel_rooflines(pkg, a, dev, pk):
         pw, mw, sw, cw = pkg.ops.quantize_activation(w, th, cb, bits, 64)
         xh = [pkg.ops.quantize_activation_dequant(x, th, cb, bits, 64, torch.float16) for x in xs]
         G = K // 64
+        staged = M >= pkg.WeightStager.min_rows          # the route the model takes at this batch size
+        w16 = pkg.ops.unpack_weight_f16(pw, mw, sw, cw, cb, bits, 64)
+        quant = lambda i: pkg.ops.quantize_activation_dequant(xs[i % rot], th, cb, bits, 64, torch.float16)  # noqa: E731
+        packed_gemm = lambda a_op: pkg.ops.packed_weight_gemm(a_op, pw, mw, sw, cw, cb, bias, bits, 64, torch.float16)  # noqa: E731
+        dense_gemm = lambda a_op: pkg.ops.dense_weight_gemm(a_op, w16, bias, torch.float16)  # noqa: E731
+        gemm = dense_gemm if staged else packed_gemm
         # In the model the GEMM's activation operand was written by the quantizer just before, so it is read
         # from L2; time the pair and the quantizer alone, and take the GEMM as the difference.  The four
-        # rotating inputs (and as many outputs) keep the working set of consecutive calls apart.
-        qms = timed(lambda i: pkg.ops.quantize_activation_dequant(xs[i % rot], th, cb, bits, 64, torch.float16))
-        pair_ms = timed(lambda i: pkg.ops.packed_weight_gemm(
-            pkg.ops.quantize_activation_dequant(xs[i % rot], th, cb, bits, 64, torch.float16),
-            pw, mw, sw, cw, cb, bias, bits, 64, torch.float16))
-        cold_ms = timed(lambda i: pkg.ops.packed_weight_gemm(xh[i % rot], pw, mw, sw, cw, cb, bias, bits, 64, torch.float16))
+        # rotating inputs (and as many outputs) keep the working set of consecutive calls apart.  In the staged
+        # route the weight was unpacked on the side stream during the previous layer: that kernel is timed alone.
+        qms = timed(quant)
+        pair_ms = timed(lambda i: gemm(quant(i)))
+        cold_ms = timed(lambda i: gemm(xh[i % rot]))
+        other_ms = timed(lambda i: (packed_gemm if staged else dense_gemm)(quant(i))) - qms
+        unpack_ms = timed(lambda i: pkg.ops.unpack_weight_f16(pw, mw, sw, cw, cb, bits, 64, out=w16))
+        # what a plain device copy of the quantizer's bytes (M*K fp16 in, as many out) takes in the same harness:
+        # at 10-40 MB a copy is far from the large-copy peak, so this is the fairer yardstick for the quantizer
+        copy_ms = timed(lambda i: xh[(i + 1) % rot].copy_(xs[i % rot]))
+        aq_copy_ms += copy_ms
         ms = pair_ms - qms
-        nbytes = M * K * 2 + N * K * bits // 8 + N * G * 12 + (2 ** bits) * 4 + N * 4 + M * N * 2
+        wbytes = N * K * 2 if staged else N * K * bits // 8 + N * G * 12 + (2 ** bits) * 4
+        nbytes = M * K * 2 + wbytes + N * 4 + M * N * 2
         flop = 2.0 * M * N * K
         qbytes = M * K * 2 * 2
         per_layer.append(dict(layer=name, M=M, K=K, N=N, ms=ms, tflops=flop / ms / 1e9, gbs=nbytes / ms / 1e6,
-                              act_quant_ms=qms, act_quant_gbs=qbytes / qms / 1e6, gemm_ms_operand_from_hbm=cold_ms))
+                              act_quant_ms=qms, act_quant_gbs=qbytes / qms / 1e6, gemm_ms_operand_from_hbm=cold_ms,
+                              weight_unpack_ms=unpack_ms, copy_of_act_quant_bytes_ms=copy_ms,
+                              **{("packed_weight_gemm_ms" if staged else "dense_weight_gemm_ms"): other_ms}))
         tot_flop, tot_ms, tot_bytes = tot_flop + flop, tot_ms + ms, tot_bytes + nbytes
         aq_bytes, aq_ms = aq_bytes + qbytes, aq_ms + qms
     achieved = tot_flop / tot_ms / 1e9
-    # DRAM bytes (read + write) per launch from one ncu capture of this command's GEMM launches, DeiT-S W4A4
-    # batch 64: the activation and the packed weight are read once; the result is still in the 126 MB L2 when
-    # the kernel ends, so it does not show up as DRAM writes of this kernel.
-    captured = {("qkv", 12608, 4): 10.06e6, ("proj", 12608, 4): 9.85e6, ("fc1", 12608, 4): 10.16e6, ("fc2", 12608, 4): 39.20e6}
-    tr = [captured.get((l["layer"], M, bits)) for l in per_layer]
-    traffic = sum(tr) / len(tr) if tr and all(t is not None for t in tr) and a.model == "deit_small" else None
-    out["roofline"] = {"kernel": "packed_weight_gemm_ws_kernel", "bound": "tensor", "achieved": achieved,
+    staged = M >= pkg.WeightStager.min_rows
+    kernel = "dense_weight_gemm_pair_kernel" if staged else "packed_weight_gemm_ws_kernel"
+    # DRAM bytes (read + write) per launch from ncu captures of this command's GEMM launches: a small table under
+    # profiles/, keyed by model, batch, bits and kernel (null when no capture covers this workload)
+    traffic = None
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles", "ncu_dram_bytes.json")) as f:
+            table = json.load(f)
+        row = table.get(f"{a.model}/b{a.batch}/w{bits}/{kernel}")
+        if row is not None and all(l["layer"] in row for l in per_layer):
+            traffic = sum(row[l["layer"]] for l in per_layer) / len(per_layer)
+    except (OSError, ValueError):
+        pass
+    out["roofline"] = {"kernel": kernel, "bound": "tensor", "achieved": achieved,
                        "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"], "traffic": traffic,
                        "peak_source": pk["source"] + " cuBLAS bf16 burst",
                        "algorithmic_bytes_per_launch_avg": tot_bytes / len(per_layer),
                        "ms_per_launch_avg": tot_ms / len(per_layer),
+                       "weight_route": "staged: unpacked on a side stream during the previous layer, read by TMA" if staged
+                                       else "packed: rebuilt inside the GEMM kernel",
                        "per_layer": per_layer}
     aq = aq_bytes / aq_ms / 1e6
-    out["roofline_act_quant"] = {"kernel": "act_quant_kernel", "bound": "hbm", "achieved": aq, "peak": pk["hbm_gbs"],
+    out["roofline_act_quant"] = {"kernel": "act_quant_v2_kernel (qkv / proj / fc1 inputs), act_quant_v4_kernel with GELU (fc2 input)", "bound": "hbm", "achieved": aq, "peak": pk["hbm_gbs"],
                                  "unit": "GB/s", "frac": aq / pk["hbm_gbs"], "traffic": None,
-                                 "peak_source": pk["source"] + " copy"}
+                                 "peak_source": pk["source"] + " copy",
+                                 "frac_of_same_size_copy": aq_copy_ms / aq_ms}
     return out
 
 
@@ -501,7 +525,9 @@ def run_gpu_arm(a):
                     "h2d_bytes_per_step": host_batches[0].numel() * 2, "d2h_bytes_per_step": host_logits.numel() * 2,
                     "ms_per_step": ms_e2e / a.steps},
             # per forward: one quantizer and one GEMM per packed linear, one add+LayerNorm kernel per norm
-            "gpu_launches": (2 * n_lin + 2 * pkg.DEIT_CONFIGS[a.model][2] + 1) * a.steps,
+            # (a third per linear at batch sizes that take the staged weight route: the weight unpack)
+            "gpu_launches": ((3 if B * TOKENS >= pkg.WeightStager.min_rows and pkg.ARCQPackedLinearOnTheFly.weight_form == "auto"
+                              else 2) * n_lin + 2 * pkg.DEIT_CONFIGS[a.model][2] + 1) * a.steps,
             "clocks": clocks, "device_status": status,
         }
         if gather_check is not None:

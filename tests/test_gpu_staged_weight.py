@@ -45,7 +45,10 @@ def test_unpacked_weight_and_dense_gemm_equal_the_packed_weight_gemm(pkg, oracle
 @pytest.mark.parametrize("options", [dict(), dict(ARCQ_PAIR_BN=32), dict(ARCQ_PAIR_BN=64), dict(ARCQ_PAIR_BN=96),
                                      dict(ARCQ_PAIR_BN=128), dict(ARCQ_PAIR_BN=192), dict(ARCQ_PAIR_BN=256),
                                      dict(ARCQ_PAIR_KS=1), dict(ARCQ_PAIR_KS=3), dict(ARCQ_PAIR_SA=2),
-                                     dict(ARCQ_PAIR_BN=192, ARCQ_PAIR_KS=1, ARCQ_PAIR_SA=5), dict(ARCQ_PAIR_PAIRS=7)])
+                                     dict(ARCQ_PAIR_BN=192, ARCQ_PAIR_KS=1, ARCQ_PAIR_SA=5), dict(ARCQ_PAIR_PAIRS=7),
+                                     dict(ARCQ_PAIR_STATIONARY=1), dict(ARCQ_PAIR_STATIONARY=0),
+                                     dict(ARCQ_PAIR_STATIONARY=1, ARCQ_PAIR_BN=64), dict(ARCQ_PAIR_STATIONARY=1, ARCQ_PAIR_KS=1),
+                                     dict(ARCQ_PAIR_STATIONARY=1, ARCQ_PAIR_BN=128, ARCQ_PAIR_PAIRS=5)])
 @pytest.mark.parametrize("M,K,N", [(256, 64, 768), (2500, 384, 768), (64 * 197, 384, 1536), (5000, 1536, 768)])
 def test_dense_pair_kernel_equals_the_one_cta_kernel(pkg, cuda_device, M, K, N, options):
     gen = torch.Generator().manual_seed(M + K + N)
@@ -115,3 +118,76 @@ def test_whole_model_logits_do_not_depend_on_the_weight_route(pkg, cuda_device, 
             assert torch.equal(y_alone, layer(h))
     finally:
         cls.weight_form = saved
+
+
+@pytest.mark.parametrize("M,K,bits", [(5, 192, 4), (300, 384, 4), (64 * 197, 384, 4), (64 * 197, 384, 3), (1000, 768, 4),
+                                      (777, 1024, 2), (2600, 192, 3)])
+def test_layernorm_fused_with_the_quantizer(pkg, oracle, cuda_device, M, K, bits):
+    """Residual add + LayerNorm + activation quantizer in one kernel.  The residual sum equals the separate
+    kernel's; the LayerNorm output (returned on request) is a valid LayerNorm (within one fp16 step of torch's and
+    of the separate kernel's, equal to the latter almost everywhere); and the reconstruction is, bit for bit, what
+    the quantizer kernel -- and the CPU oracle -- make of that LayerNorm output."""
+    dev = cuda_device
+    gen = torch.Generator().manual_seed(M + K + bits)
+    x = torch.randn(M, K, generator=gen).half().to(dev)
+    y = (torch.randn(M, K, generator=gen) * 0.5).half().to(dev)
+    norm = torch.nn.LayerNorm(K, eps=1e-6).to(dev)
+    with torch.no_grad():
+        norm.weight.copy_(1 + 0.1 * torch.randn(K, generator=gen))
+        norm.bias.copy_(0.05 * torch.randn(K, generator=gen))
+    cb = torch.sort(torch.randn(2 ** bits, generator=gen) * 1.1)[0].to(dev)
+    th = (cb[:-1] + cb[1:]) / 2
+    for yy in (y, None):
+        s0, h0 = pkg.ops.add_layernorm(x, yy, norm)
+        s1, xh1, h1 = pkg.ops.add_layernorm_quant(x, yy, norm, th, cb, bits, 64, want_h=True)
+        s2, xh2 = pkg.ops.add_layernorm_quant(x, yy, norm, th, cb, bits, 64)
+        assert torch.equal(s0, s1) and torch.equal(s1, s2) and torch.equal(xh1, xh2)
+        with torch.no_grad():
+            ref = torch.nn.functional.layer_norm(s0.float(), (K,), norm.weight.float(), norm.bias.float(), 1e-6)
+        step = 2.0 ** -10 * float(ref.abs().max())                       # one fp16 step at the largest magnitude
+        assert float((h1.float() - ref).abs().max()) <= step
+        assert float((h1.float() - h0.float()).abs().max()) <= step and float((h1 == h0).float().mean()) > 0.999
+        want = pkg.ops.quantize_activation_dequant(h1, th, cb, bits, 64, torch.float16)
+        assert torch.equal(xh1, want)
+    # rows do not depend on the tile they fall in
+    part = pkg.ops.add_layernorm_quant(x[: min(M, 37)].contiguous(), y[: min(M, 37)].contiguous(), norm, th, cb, bits, 64)[1]
+    full = pkg.ops.add_layernorm_quant(x, y, norm, th, cb, bits, 64)[1]
+    assert torch.equal(full[: part.shape[0]], part)
+    # and against the CPU oracle on a few rows of the returned LayerNorm output
+    rows = slice(0, min(M, 16))
+    _, _, h = pkg.ops.add_layernorm_quant(x, y, norm, th, cb, bits, 64, want_h=True)
+    hn = h[rows].float().cpu().numpy()
+    codes, mu, sg, cs = oracle.quantize(hn, th.cpu().numpy(), cb.cpu().numpy(), 64)
+    want_np = oracle.dequant(codes, mu, sg, cb.cpu().numpy(), 64).astype(np.float16)
+    assert np.array_equal(full[rows].cpu().numpy(), want_np)
+    assert pkg.ops.device_status() == 0
+
+
+def test_model_with_the_fused_norm_quantizer(pkg, cuda_device):
+    """The ViT skeleton with ``fuse_norm_quant``: same graph, one kernel fewer in front of qkv and fc1.  Its logits
+    differ from the unfused forward only through the few LayerNorm outputs that round the other way (amplified by
+    the quantizers downstream, like any other one-step perturbation), so they are compared layer by layer: with the
+    fused kernel fed the same input, the first block's qkv output is the unfused one wherever h agreed."""
+    dev = cuda_device
+    gen = torch.Generator().manual_seed(11)
+    model = pkg.create_vit("deit_tiny", seed=2).half().to(dev)
+    x = torch.randn(8, 3, 224, 224, generator=gen).half().to(dev)
+    saved = pkg.VisionTransformer.fuse_norm_quant
+    try:
+        with torch.no_grad():
+            model = pkg.quantise_model(model, x, 4)
+            pkg.VisionTransformer.fuse_norm_quant = False
+            y0 = model(x).clone()
+            pkg.VisionTransformer.fuse_norm_quant = True
+            y1 = model(x).clone()
+            g1 = pkg.GraphedModel(model, x)(x).clone()
+        assert torch.equal(y1, g1)
+        assert pkg.ops.device_status() == 0
+        assert bool(torch.isfinite(y1).all())
+        rms = float(y0.float().pow(2).mean().sqrt())
+        assert float((y1.float() - y0.float()).pow(2).mean().sqrt()) < 0.5 * rms
+        lin = model.blocks[0].attn.qkv
+        with pytest.raises(ValueError):
+            lin(torch.zeros(4, lin.in_features, dtype=torch.float16, device=dev), pre_gelu=True, pre_quantized=True)
+    finally:
+        pkg.VisionTransformer.fuse_norm_quant = saved
