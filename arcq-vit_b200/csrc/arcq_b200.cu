@@ -568,7 +568,9 @@ int max_resident_dense_pairs(size_t smem) {
 // Cost model in microseconds, same constants as the packed-weight pair kernel's: a tile is bound by its output
 // stores (about 22 GB/s per SM) or by the issuing thread, and every slab streams the whole activation from L2.
 bool choose_pair_dense_config(long long M, long long N, long long K, bool y_f32, PairDenseConfig* c) {
-  if (opt(O_PAIR) == 0 || M < opt(O_PAIR_MIN_M)) return false;
+  // No row threshold (ARCQ_PAIR_MIN_M gates the packed-weight pair kernel only): with nothing to rebuild, the pair
+  // form measured faster than the one-CTA form from one row tile on (DeiT-S batch 1: 0.55 against 0.68 ms).
+  if (opt(O_PAIR) == 0) return false;
   const int G = static_cast<int>(K / 64);
   if (G < 1) return false;
   const long long tiles_m = (M + arcq::kPairTileM - 1) / arcq::kPairTileM;
@@ -594,9 +596,17 @@ bool choose_pair_dense_config(long long M, long long N, long long K, bool y_f32,
   double best_cost = 0;
   bool found = false;
   PairDenseConfig best = {};
+  // One or two row tiles (batch 1-2 of a ViT): the launch is a latency chain, not a throughput problem.  The
+  // narrowest slab that still gives every (tile, slab) its own pair spreads the epilogue over the most SMs
+  // (DeiT-S batch 1: 0.528 ms with 32-column slabs against 0.555 ms with the throughput model's choice).
+  int narrow_bn = 0;
+  if (tiles_m <= 2 && opt(O_PAIR_BN) == 0)
+    for (int bn : cand)
+      if (N % bn == 0 && (N / bn) * tiles_m <= max_pairs) narrow_bn = bn;      // candidates descend: keeps the narrowest
   for (int bn : cand) {
     if (N % bn != 0) continue;
     if (opt(O_PAIR_BN) > 0 && bn != opt(O_PAIR_BN)) continue;
+    if (narrow_bn != 0 && bn != narrow_bn) continue;
     const long long slabs = N / bn;
     if (slabs > max_pairs) continue;
     long long per = max_pairs / slabs;

@@ -9,6 +9,8 @@ Bad arguments raise ``RuntimeError`` like the reference's ``TORCH_CHECK``s.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _cabi
@@ -99,6 +101,12 @@ def quantize_activation_dequant(x: torch.Tensor, thresholds: torch.Tensor, codeb
     return out
 
 
+# How ``arcq_linear_forward`` runs: "auto" takes two kernels (activation reconstruction, then the packed-weight
+# GEMM) for every shape the packed-weight GEMM accepts, whatever the number of rows, so that a row's result does
+# not depend on the batch it is computed in; "single" always runs the one kernel that rebuilds both operands.
+LINEAR_FORWARD_ROUTE = os.environ.get("ARCQ_LINEAR_ROUTE", "auto")
+
+
 def arcq_linear_forward(packed_x, x_center, x_scale, x_code_sum, packed_w, w_center, w_scale, w_code_sum,
                         act_codebook, w_codebook, bias, bits: int, group_size: int, in_features: int,
                         out_features: int, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
@@ -125,6 +133,13 @@ def arcq_linear_forward(packed_x, x_center, x_scale, x_code_sum, packed_w, w_cen
         b = _dev(bias, "bias", torch.float32)
         if b.numel() != out_features:
             raise RuntimeError("bias must have out_features entries")
+    if (LINEAR_FORWARD_ROUTE != "single" and M > 0
+            and packed_weight_gemm_supported(in_features, out_features, bits, group_size)):
+        # Two kernels instead of one: reconstruct the activation once into an fp16 matrix (what the quantizer's
+        # reconstruction output holds, bit for bit) and run the GEMM that rebuilds only the weight.  The single
+        # kernel below rebuilds both operands inside every tile, which costs 4-6x more on large M.
+        x_hat = dequant(packed_x, f[0], f[1], f[2], f[6], bits, group_size, torch.float16)
+        return packed_weight_gemm(x_hat, packed_w, f[3], f[4], f[5], f[7], b, bits, group_size, out_dtype)
     y = torch.empty((M, out_features), dtype=out_dtype, device=packed_x.device)
     if M == 0:
         return y

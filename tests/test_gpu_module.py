@@ -166,3 +166,40 @@ def test_operators_with_the_reference_extension_signatures(pkg, golden, cuda_dev
                                       layer.weight_code_sum, layer.product_table, layer.bias, 64)
     assert float((got8 - want).abs().max()) < 1e-3 * rms
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("bits", [4, 3])
+def test_linear_forward_two_kernel_route_agrees_with_the_single_kernel(pkg, cuda_device, bits):
+    """``arcq_linear_forward`` reconstructs the activation once and runs the packed-weight GEMM; the single kernel
+    (``ARCQ_LINEAR_ROUTE=single``, and every shape the packed-weight GEMM declines) rebuilds both operands per tile.  Same operands, same products: outputs agree to fp16 rounding
+    of the activation reconstruction (fused multiply-add in one, three rounded steps in the other)."""
+    ops = pkg.ops
+    dev = cuda_device
+    gen = torch.Generator().manual_seed(40 + bits)
+    M, K, N = 3000, 384, 768
+    cb = torch.sort(torch.randn(2 ** bits, generator=gen) * 1.1)[0].to(dev)
+    th = (cb[:-1] + cb[1:]) / 2
+    x = torch.randn(M, K, generator=gen).to(dev)
+    w = (torch.randn(N, K, generator=gen) * 0.03).to(dev)
+    bias = torch.randn(N, generator=gen).to(dev) * 0.01
+    px, mu, sg, cs = ops.quantize_activation(x, th, cb, bits, 64)
+    pw, mw, sw, cw = ops.quantize_activation(w, th, cb, bits, 64)
+    saved = ops.LINEAR_FORWARD_ROUTE
+    try:
+        ops.LINEAR_FORWARD_ROUTE = "single"
+        y1 = ops.arcq_linear_forward(px, mu, sg, cs, pw, mw, sw, cw, cb, cb, bias, bits, 64, K, N)
+        ops.LINEAR_FORWARD_ROUTE = "auto"
+        y2 = ops.arcq_linear_forward(px, mu, sg, cs, pw, mw, sw, cw, cb, cb, bias, bits, 64, K, N)
+        small = ops.arcq_linear_forward(px[:100].contiguous(), mu[:100].contiguous(), sg[:100].contiguous(),
+                                        cs[:100].contiguous(), pw, mw, sw, cw, cb, cb, bias, bits, 64, K, N)
+    finally:
+        ops.LINEAR_FORWARD_ROUTE = saved
+    assert y1.dtype == y2.dtype == torch.float32
+    xa = ops.dequant(px, mu, sg, cs, cb, bits, 64, torch.float32).double()
+    wa = ops.dequant(pw, mw, sw, cw, cb, bits, 64, torch.float32).double()
+    ref = xa @ wa.T + bias.double()
+    rms = float(ref.pow(2).mean().sqrt())
+    assert float((y1.double() - ref).abs().max()) < 6e-3 * rms
+    assert float((y2.double() - ref).abs().max()) < 6e-3 * rms
+    assert torch.equal(small, y2[:100])            # rows do not depend on the batch they are computed in
+    assert ops.device_status() == 0
