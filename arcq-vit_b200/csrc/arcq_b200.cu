@@ -22,6 +22,7 @@
 #include "gemm_pair_dense.cuh"
 #include "add_layernorm.cuh"
 #include "ln_act_quant.cuh"
+#include "attention.cuh"
 #include <cudaTypedefs.h>
 
 namespace {
@@ -1076,6 +1077,59 @@ int arcq_add_layernorm_act_quant(const void* x, const void* y, const float* gamm
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "add_layernorm_act_quant launch");
   return ARCQ_OK;
+}
+
+static int launch_attention(const void* qkv, int64_t B, int64_t T, int64_t H, int head_dim, const float* thresholds,
+                            const float* codebook, int bits, void* out, void* stream) {
+  if (qkv == nullptr || out == nullptr) return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (head_dim != 64) return fail(ARCQ_E_UNSUPPORTED, "head_dim %d: only 64 is built", head_dim);
+  if (B < 0 || T <= 0 || H <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape B=%lld T=%lld H=%lld", (long long)B, (long long)T, (long long)H);
+  if (T > arcq::kAttnMaxT) return fail(ARCQ_E_TOO_LARGE, "sequences longer than %d tokens are not built", arcq::kAttnMaxT);
+  if (B * H > 0x7fffffffLL) return fail(ARCQ_E_TOO_LARGE, "too many (image, head) pairs");
+  if (!aligned(qkv, 16) || !aligned(out, 16)) return fail(ARCQ_E_ALIGN, "qkv and out must be 16-byte aligned");
+  if (B == 0) return ARCQ_OK;
+  arcq::AttnParams p;
+  p.qkv = static_cast<const __half*>(qkv);
+  p.out = static_cast<__half*>(out);
+  p.B = static_cast<int>(B); p.T = static_cast<int>(T); p.H = static_cast<int>(H);
+  p.tp = static_cast<int>((T + 15) / 16 * 16);
+  p.thresholds = thresholds;
+  p.codebook = codebook;
+  const size_t smem = arcq::attn_smem_bytes(p.tp);
+  const unsigned grid = static_cast<unsigned>(B * H);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define ARCQ_LAUNCH_ATTN(Q, BT)                                                                                      \
+  do {                                                                                                                \
+    static thread_local int done_dev = -1;                                                                            \
+    int dev = 0;                                                                                                      \
+    cudaGetDevice(&dev);                                                                                              \
+    if (done_dev != dev) {                                                                                            \
+      cudaFuncSetAttribute(arcq::attention_kernel<Q, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
+                           static_cast<int>(arcq::attn_smem_bytes(arcq::kAttnMaxT)));                                 \
+      done_dev = dev;                                                                                                 \
+    }                                                                                                                 \
+    launch_pdl(arcq::attention_kernel<Q, BT>, grid, arcq::kAttnThreads, smem, st, p);                                 \
+  } while (0)
+  if (thresholds == nullptr) ARCQ_LAUNCH_ATTN(false, 4);
+  else if (bits == 4) ARCQ_LAUNCH_ATTN(true, 4);
+  else if (bits == 3) ARCQ_LAUNCH_ATTN(true, 3);
+  else ARCQ_LAUNCH_ATTN(true, 2);
+#undef ARCQ_LAUNCH_ATTN
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "attention launch");
+  return ARCQ_OK;
+}
+
+int arcq_attention(const void* qkv, int64_t B, int64_t T, int64_t H, int head_dim, void* out, void* stream) {
+  return launch_attention(qkv, B, T, H, head_dim, nullptr, nullptr, 4, out, stream);
+}
+
+int arcq_attention_act_quant(const void* qkv, int64_t B, int64_t T, int64_t H, int head_dim, const float* thresholds,
+                             const float* codebook, int bits, int group_size, void* xhat, void* stream) {
+  if (thresholds == nullptr || codebook == nullptr) return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
+  if (group_size != 64) return fail(ARCQ_E_UNSUPPORTED, "group_size %d: only 64 is built", group_size);
+  return launch_attention(qkv, B, T, H, head_dim, thresholds, codebook, bits, xhat, stream);
 }
 
 int arcq_unpack_codes(const uint8_t* packed, int64_t rows, int64_t length, int bits, uint8_t* codes_out, void* stream) {

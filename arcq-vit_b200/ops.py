@@ -247,6 +247,29 @@ def add_layernorm_quant(x: torch.Tensor, y, norm: torch.nn.LayerNorm, thresholds
     return out + (h.reshape(shape),) if want_h else out
 
 
+def attention(qkv: torch.Tensor, batch: int, tokens: int, heads: int, thresholds: torch.Tensor = None,
+              codebook: torch.Tensor = None, bits: int = 4, group_size: int = 64) -> torch.Tensor:
+    """softmax(q k^T / sqrt(64)) v for every (image, head) of ``qkv`` [batch*tokens, 3*heads*64] fp16 (the qkv linear's
+    output); returns [batch*tokens, heads*64] fp16, heads side by side (timm ``Attention.forward`` between qkv and
+    proj).  With ``thresholds`` / ``codebook`` (those of the proj linear) the result is quantised on the way out: the
+    return value is the reconstruction ``quantize_activation_dequant`` would give, for ``proj(x, pre_quantized=True)``."""
+    lib = _cabi.load()
+    C = heads * 64
+    q2 = _dev(qkv.reshape(-1, 3 * C), "qkv", torch.float16)
+    if q2.shape[0] != batch * tokens:
+        raise RuntimeError(f"qkv has {q2.shape[0]} rows, expected {batch} x {tokens}")
+    out = torch.empty((batch * tokens, C), dtype=torch.float16, device=q2.device)
+    if thresholds is None:
+        rc = lib.arcq_attention(q2.data_ptr(), batch, tokens, heads, 64, out.data_ptr(), _stream())
+        _check(rc, "arcq_attention")
+    else:
+        thresholds, codebook = _dev(thresholds, "thresholds", torch.float32), _dev(codebook, "codebook", torch.float32)
+        rc = lib.arcq_attention_act_quant(q2.data_ptr(), batch, tokens, heads, 64, thresholds.data_ptr(),
+                                          codebook.data_ptr(), bits, group_size, out.data_ptr(), _stream())
+        _check(rc, "arcq_attention_act_quant")
+    return out
+
+
 def unpack_codes_u8(packed: torch.Tensor, bits: int, length: int) -> torch.Tensor:
     """uint8 [R, ceil(length*bits/8)] -> uint8 [R, length] (reference: arcq_pack_kernel.cu:136-157)."""
     lib = _cabi.load()

@@ -32,6 +32,10 @@ DEIT_CONFIGS: Dict[str, Tuple[int, int, int]] = {
 
 
 class Attention(nn.Module):
+    # "kernel": this package's attention kernel (heads of 64, at most 256 tokens, fp16 on a GPU), which also runs
+    # proj's activation quantizer when proj can take a reconstructed input; "sdpa": the library attention.
+    implementation = os.environ.get("ARCQ_ATTENTION", "sdpa")
+
     def __init__(self, dim: int, heads: int):
         super().__init__()
         self.num_heads = heads
@@ -41,6 +45,15 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, pre_quantized: bool = False) -> torch.Tensor:
         B, T, C = x.shape
         qkv = self.qkv(x, pre_quantized=True) if pre_quantized else self.qkv(x)
+        if (self.implementation == "kernel" and qkv.is_cuda and qkv.dtype == torch.float16 and C == 64 * self.num_heads
+                and T <= 256):
+            from . import ops
+            proj = self.proj
+            if isinstance(proj, ARCQPackedLinearOnTheFly) and proj.takes_reconstructed_input():
+                xh = ops.attention(qkv, B, T, self.num_heads, proj.activation_thresholds, proj.activation_codebook,
+                                   proj.bits, proj.group_size)
+                return proj(xh.reshape(B, T, C), pre_quantized=True)
+            return proj(ops.attention(qkv, B, T, self.num_heads).reshape(B, T, C))
         qkv = qkv.reshape(B, T, 3, self.num_heads, C // self.num_heads).permute(2, 0, 3, 1, 4)
         o = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2])
         return self.proj(o.transpose(1, 2).reshape(B, T, C))

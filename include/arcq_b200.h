@@ -216,6 +216,21 @@ int arcq_add_layernorm_act_quant(const void* x, const void* y, const float* gamm
                                  int group_size, void* sum_out, void* h_out, void* xhat, void* stream);
 
 /*
+ * Multi-head self-attention on the output of the packed qkv linear, for short sequences (T <= 256) and heads of 64:
+ * qkv [B*T, 3*H*64] fp16 (q | k | v), out [B*T, H*64] fp16 = softmax(q k^T / 8) v with the heads side by side --
+ * what timm's Attention.forward computes between its qkv and proj linears with F.scaled_dot_product_attention.
+ * Products on tensor cores with fp32 accumulation, softmax in fp32, probabilities rounded to fp16 for the second
+ * product (as the library attention kernels do).
+ *
+ * arcq_attention_act_quant additionally runs the activation quantizer of the proj linear on the result (a head's 64
+ * outputs are one quantizer group): xhat is, bit for bit, what arcq_act_quant reconstructs from arcq_attention's out.
+ */
+int arcq_attention(const void* qkv, int64_t B, int64_t T, int64_t H, int head_dim, void* out, void* stream);
+int arcq_attention_act_quant(const void* qkv, int64_t B, int64_t T, int64_t H, int head_dim,
+                             const float* thresholds, const float* codebook, int bits, int group_size,
+                             void* xhat, void* stream);
+
+/*
  * Unpack codes to one byte per code.  Replaces unpack_codes_u8_cuda,
  * EXT/arcq_pack_kernel.cu:136-157 (kernel :74-90); the int64 variant
  * unpack_codes_cuda (:113-134) is this plus a widening on the host side.
