@@ -122,7 +122,6 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
                                                                    float* __restrict__ codesum_out,
                                                                    XH* __restrict__ xhat) {
   pdl_launch_dependents();   // the next kernel of the stream may start its set-up
-  pdl_wait();                // the input may be the previous kernel's output
 
   constexpr int L = 1 << BITS;
   constexpr int kPitch = Aq2Row<T>::kPitch, kRowBytes = Aq2Row<T>::kBytes;
@@ -213,6 +212,10 @@ __global__ void __launch_bounds__(kAq2Threads, 4) act_quant_v2_kernel(const T* _
     cp_async_commit();
   };
 
+  // Everything above reads only the layer's thresholds and codebook, which no kernel of this library writes: when
+  // launched as a programmatic dependent, the block builds its tables while the previous kernel is still running
+  // and waits for it here, before the first read of x.
+  pdl_wait();
   long long tile = blockIdx.x;
   int buf = 0;
   if (tile < tiles) issue_tile(tile, 0);

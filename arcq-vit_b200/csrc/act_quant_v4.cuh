@@ -64,7 +64,6 @@ __global__ void __launch_bounds__(kAq4Threads, 4) act_quant_v4_kernel(const T* _
                                                                    float* __restrict__ codesum_out,
                                                                    T* __restrict__ xhat) {
   pdl_launch_dependents();   // the next kernel of the stream may start its set-up
-  pdl_wait();                // the input may be the previous kernel's output
 
   static_assert(sizeof(T) == 2, "two-lane kernel is written for 16-bit element types");
   constexpr int L = 1 << BITS;
@@ -147,6 +146,10 @@ __global__ void __launch_bounds__(kAq4Threads, 4) act_quant_v4_kernel(const T* _
 
   const char* const col = reinterpret_cast<const char*>(s_table + gl);
   const char* const cbcol = reinterpret_cast<const char*>(s_cbt + gl);
+  // Everything above reads only the layer's thresholds and codebook, which no kernel of this library writes: when
+  // launched as a programmatic dependent, the block builds its tables while the previous kernel is still running
+  // and waits for it here, before the first read of x.
+  pdl_wait();
   long long tile = blockIdx.x;
   int buf = 0;
   if (tile < tiles) issue_tile(tile, 0);

@@ -108,7 +108,6 @@ __global__ void __launch_bounds__(256) add_layernorm_rows_kernel(const __half* _
                                                                  long long M, __half* __restrict__ sum_out,
                                                                  __half* __restrict__ h_out) {
   pdl_launch_dependents();   // the next kernel of the stream may start its set-up
-  pdl_wait();                // the input may be the previous kernel's output
 
   constexpr int K = LANES * 24, kRowsPerWarp = 32 / LANES;
   const int lane = threadIdx.x & 31, l = lane % LANES, sub = lane / LANES;
@@ -125,6 +124,7 @@ __global__ void __launch_bounds__(256) add_layernorm_rows_kernel(const __half* _
     bb[i][0] = b0.x; bb[i][1] = b0.y; bb[i][2] = b0.z; bb[i][3] = b0.w;
     bb[i][4] = b1.x; bb[i][5] = b1.y; bb[i][6] = b1.z; bb[i][7] = b1.w;
   }
+  pdl_wait();                // gamma and beta are the layer's constants; x and y may be the previous kernel's output
   const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
   const long long first = (static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * kRowsPerWarp;
   for (long long row0 = first; row0 < M; row0 += warps * kRowsPerWarp) {
