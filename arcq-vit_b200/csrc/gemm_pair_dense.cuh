@@ -40,6 +40,14 @@ struct PairDenseParams {
 };
 
 constexpr int kPairDenseThreads = (2 + kPairEpiWarps) * 32;
+// Staging blocks (2 KB: 32 rows x 64 bytes) per epilogue warp; a block can be rewritten once the TMA store that
+// reads it has done so.  Four blocks instead of two measured slower on every DeiT-S shape (qkv 13.6 -> 15.5 us,
+// fc2 17.5 -> 22.3 us): the 32 KB they take away from the operand stages cost more than deeper stores gain.
+#ifndef ARCQ_DENSE_STAGE_BLOCKS
+#define ARCQ_DENSE_STAGE_BLOCKS 2
+#endif
+constexpr int kDenseStageBlocks = ARCQ_DENSE_STAGE_BLOCKS;
+constexpr uint32_t kPairDenseEpiStageBytes = kPairEpiWarps * kDenseStageBlocks * 2048;
 
 struct PairDenseSmem {
   uint32_t stages, slab, stage, misc, total;
@@ -52,7 +60,7 @@ __host__ __device__ inline PairDenseSmem pair_dense_smem_layout(int bn, int sa, 
   s.stages = 0;
   s.slab = static_cast<uint32_t>(sa) * stage_bytes;
   s.stage = s.slab + (stationary ? static_cast<uint32_t>(G) * wtile : 0u);
-  s.misc = s.stage + kPairEpiStageBytes;
+  s.misc = s.stage + kPairDenseEpiStageBytes;
   s.total = s.misc + 256 * 4 /*bias*/ + kPairDenseBarriers * 8 + 16 /*tensor-memory address*/;
   return s;
 }
@@ -234,12 +242,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairDenseThreads, 1
     const int lq = warp & 3;                          // tensor-memory lane quarter this warp may read
     const int half_id = ew >> 2;                      // which of the two warps of the quarter
     const uint32_t acc_empty_leader = mapa_shared(acc_empty, 0);
-    uint8_t* const stg = sStage + ew * 4096;
+    uint8_t* const stg = sStage + ew * (kDenseStageBlocks * 2048);
     const int cw = p.y_f32 ? 16 : 32;
     const bool f32 = p.y_f32 != 0;
-    uint32_t blk = 0;      // staging block of the next store; the two blocks alternate from store to store
+    uint32_t blk = 0;      // staging block of the next store; the blocks are used in turn
     auto emit = [&](const uint32_t (&acc)[32], int c0, int row0) {
-      if (lane == 0) tma_store_wait_read_1();      // the store issued two stores ago has read this block
+      if (lane == 0) tma_store_wait_read_n<kDenseStageBlocks - 1>();   // the store that last used this block has read it
       __syncwarp();
       uint8_t* const rowp = stg + blk * 2048 + lane * 64;
       const int sw = (lane >> 1) & 3;
@@ -272,7 +280,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairDenseThreads, 1
         tma_store_2d(&tm_y, stg + blk * 2048, n0 + c0, row0);     // rows beyond M are clipped
         tma_store_commit();
       }
-      blk ^= 1;
+      blk = (blk + 1 == kDenseStageBlocks) ? 0 : blk + 1;
     };
     auto load = [&](uint32_t (&acc)[32], uint32_t taddr) {
       if (f32) tmem_ld_32x16(taddr, *reinterpret_cast<uint32_t(*)[16]>(&acc[0]));

@@ -140,6 +140,9 @@ __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk
 // all but the newest N groups have finished READING shared memory (their buffers may be overwritten)
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void tma_store_wait_read_n() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
 // 1-D bulk copy global -> shared, completing on an mbarrier.  Both addresses 16-byte aligned, size a
 // multiple of 16.
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
