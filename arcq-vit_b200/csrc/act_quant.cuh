@@ -117,7 +117,6 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const T* __restrict__ x,
                                                         float* __restrict__ sigma_out,
                                                         float* __restrict__ codesum_out, XH* __restrict__ xhat) {
   pdl_launch_dependents();   // the next kernel of the stream may start its set-up
-  pdl_wait();                // the input may be the previous kernel's output
 
   constexpr int L = 1 << BITS;
   __shared__ float s_th[16];
@@ -128,6 +127,7 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const T* __restrict__ x,
     s_cb[t] = (t < L) ? codebook[t] : 0.0f;
   }
   __syncthreads();
+  pdl_wait();                // the tables above are the layer's constants; x may be the previous kernel's output
 
   const int lane = threadIdx.x & 31;
   const int l = lane & 7;

@@ -97,21 +97,84 @@ __global__ void __launch_bounds__(256) add_layernorm_kernel(const __half* __rest
   }
 }
 
-// Same operation for rows of LANES * 24 values (192 / 384 / 768: the DeiT widths): LANES lanes per row, three
-// 16-byte chunks per lane, so every lane carries the same load and a warp works on 32 / LANES rows at once;
-// gamma and beta stay in registers for all the rows a lane visits.
+// One row of LANES * 24 values (192 / 384 / 768: the DeiT widths) on LANES lanes, three 16-byte chunks per lane:
+// s = fp16(x + y) (stored when asked), statistics in two passes, h = fp16((s - mean) * rstd * gamma + beta) returned
+// as the lane's three packed chunks.  `rs` is the row to read (idle sub-warps shadow the last row), `row` the row
+// to store (only if `valid`).  Shared by the LayerNorm kernel below and by the small-batch LayerNorm + quantizer
+// kernel (ln_act_quant.cuh), so that the two produce the same bits.
 template <int LANES>
-__global__ void __launch_bounds__(256) add_layernorm_rows_kernel(const __half* __restrict__ x,
-                                                                 const __half* __restrict__ y,
-                                                                 const float* __restrict__ gamma,
-                                                                 const float* __restrict__ beta, float eps,
-                                                                 long long M, __half* __restrict__ sum_out,
-                                                                 __half* __restrict__ h_out) {
-  pdl_launch_dependents();   // the next kernel of the stream may start its set-up
+__device__ __forceinline__ void layernorm_row(const __half* __restrict__ x, const __half* __restrict__ y, long long rs,
+                                              long long row, bool valid, int l, const float (&gg)[3][8],
+                                              const float (&bb)[3][8], float eps, __half* __restrict__ sum_out,
+                                              uint4 (&h)[3]) {
+  constexpr int K = LANES * 24;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + rs * K);
+  const uint4* yr = (y != nullptr) ? reinterpret_cast<const uint4*>(y + rs * K) : nullptr;
+  uint4 a[3], b[3];
+#pragma unroll
+  for (int i = 0; i < 3; ++i) a[i] = __ldg(xr + l + LANES * i);
+  if (yr != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 3; ++i) b[i] = __ldg(yr + l + LANES * i);
+  }
+  float v[3][8];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    const __half2* ah = reinterpret_cast<const __half2*>(&a[i]);
+    if (yr != nullptr) {
+      const __half2* bh = reinterpret_cast<const __half2*>(&b[i]);
+      uint4 so;
+      __half2* sh = reinterpret_cast<__half2*>(&so);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fa = __half22float2(ah[j]), fb = __half22float2(bh[j]);
+        sh[j] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);   // the fp16 sum a separate add would store
+        const float2 fs = __half22float2(sh[j]);
+        v[i][2 * j] = fs.x;
+        v[i][2 * j + 1] = fs.y;
+      }
+      if (valid && sum_out != nullptr) reinterpret_cast<uint4*>(sum_out + row * K)[l + LANES * i] = so;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fa = __half22float2(ah[j]);
+        v[i][2 * j] = fa.x;
+        v[i][2 * j + 1] = fa.y;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sum += v[i][j];
+  }
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float mean = sum * (1.0f / static_cast<float>(K));
+  float sq = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float d = v[i][j] - mean;
+      sq += d * d;
+    }
+  }
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  const float rstd = rsqrtf(sq * (1.0f / static_cast<float>(K)) + eps);
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    __half2* oh = reinterpret_cast<__half2*>(&h[i]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      oh[j] = __floats2half2_rn((v[i][2 * j] - mean) * rstd * gg[i][2 * j] + bb[i][2 * j],
+                                (v[i][2 * j + 1] - mean) * rstd * gg[i][2 * j + 1] + bb[i][2 * j + 1]);
+  }
+}
 
-  constexpr int K = LANES * 24, kRowsPerWarp = 32 / LANES;
-  const int lane = threadIdx.x & 31, l = lane % LANES, sub = lane / LANES;
-  float gg[3][8], bb[3][8];
+// gamma and beta of the lane's three chunks
+template <int LANES>
+__device__ __forceinline__ void layernorm_lane_params(const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                      int l, float (&gg)[3][8], float (&bb)[3][8]) {
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
     const int c = l + LANES * i;
@@ -124,6 +187,23 @@ __global__ void __launch_bounds__(256) add_layernorm_rows_kernel(const __half* _
     bb[i][0] = b0.x; bb[i][1] = b0.y; bb[i][2] = b0.z; bb[i][3] = b0.w;
     bb[i][4] = b1.x; bb[i][5] = b1.y; bb[i][6] = b1.z; bb[i][7] = b1.w;
   }
+}
+
+// Residual add + LayerNorm for rows of LANES * 24 values: LANES lanes per row, so every lane carries the same load
+// and a warp works on 32 / LANES rows at once; gamma and beta stay in registers for all the rows a lane visits.
+template <int LANES>
+__global__ void __launch_bounds__(256) add_layernorm_rows_kernel(const __half* __restrict__ x,
+                                                                 const __half* __restrict__ y,
+                                                                 const float* __restrict__ gamma,
+                                                                 const float* __restrict__ beta, float eps,
+                                                                 long long M, __half* __restrict__ sum_out,
+                                                                 __half* __restrict__ h_out) {
+  pdl_launch_dependents();   // the next kernel of the stream may start its set-up
+
+  constexpr int K = LANES * 24, kRowsPerWarp = 32 / LANES;
+  const int lane = threadIdx.x & 31, l = lane % LANES, sub = lane / LANES;
+  float gg[3][8], bb[3][8];
+  layernorm_lane_params<LANES>(gamma, beta, l, gg, bb);
   pdl_wait();                // gamma and beta are the layer's constants; x and y may be the previous kernel's output
   const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
   const long long first = (static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * kRowsPerWarp;
@@ -131,70 +211,11 @@ __global__ void __launch_bounds__(256) add_layernorm_rows_kernel(const __half* _
     const long long row = row0 + sub;
     const bool valid = row < M;
     const long long rs = valid ? row : M - 1;          // idle sub-warps shadow the last row, store nothing
-    const uint4* xr = reinterpret_cast<const uint4*>(x + rs * K);
-    const uint4* yr = (y != nullptr) ? reinterpret_cast<const uint4*>(y + rs * K) : nullptr;
-    uint4 a[3], b[3];
-#pragma unroll
-    for (int i = 0; i < 3; ++i) a[i] = __ldg(xr + l + LANES * i);
-    if (yr != nullptr) {
-#pragma unroll
-      for (int i = 0; i < 3; ++i) b[i] = __ldg(yr + l + LANES * i);
-    }
-    float v[3][8];
-    float sum = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 3; ++i) {
-      const __half2* ah = reinterpret_cast<const __half2*>(&a[i]);
-      if (yr != nullptr) {
-        const __half2* bh = reinterpret_cast<const __half2*>(&b[i]);
-        uint4 so;
-        __half2* sh = reinterpret_cast<__half2*>(&so);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 fa = __half22float2(ah[j]), fb = __half22float2(bh[j]);
-          sh[j] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);   // the fp16 sum a separate add would store
-          const float2 fs = __half22float2(sh[j]);
-          v[i][2 * j] = fs.x;
-          v[i][2 * j + 1] = fs.y;
-        }
-        if (valid && sum_out != nullptr) reinterpret_cast<uint4*>(sum_out + row * K)[l + LANES * i] = so;
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 fa = __half22float2(ah[j]);
-          v[i][2 * j] = fa.x;
-          v[i][2 * j + 1] = fa.y;
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) sum += v[i][j];
-    }
-#pragma unroll
-    for (int o = LANES / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float mean = sum * (1.0f / static_cast<float>(K));
-    float sq = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 3; ++i) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float d = v[i][j] - mean;
-        sq += d * d;
-      }
-    }
-#pragma unroll
-    for (int o = LANES / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    const float rstd = rsqrtf(sq * (1.0f / static_cast<float>(K)) + eps);
+    uint4 h[3];
+    layernorm_row<LANES>(x, y, rs, row, valid, l, gg, bb, eps, sum_out, h);
     if (valid) {
 #pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        uint4 o;
-        __half2* oh = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          oh[j] = __floats2half2_rn((v[i][2 * j] - mean) * rstd * gg[i][2 * j] + bb[i][2 * j],
-                                    (v[i][2 * j + 1] - mean) * rstd * gg[i][2 * j + 1] + bb[i][2 * j + 1]);
-        reinterpret_cast<uint4*>(h_out + row * K)[l + LANES * i] = o;
-      }
+      for (int i = 0; i < 3; ++i) reinterpret_cast<uint4*>(h_out + row * K)[l + LANES * i] = h[i];
     }
   }
 }

@@ -77,7 +77,7 @@ enum Opt {
   O_WS_BN, O_WS_SA, O_WS_WS, O_WS_STATIONARY, O_WS_NBB, O_WS_GRID, O_WS_TMA_STORE, O_WS_ROTATE,
   O_ACT_QUANT_V1, O_ACT_QUANT_V2, O_LN_PLAIN,
   O_PAIR, O_PAIR_MIN_M, O_PAIR_BN, O_PAIR_SA, O_PAIR_KS, O_PAIR_NBB, O_PAIR_LUT, O_PAIR_PAIRS, O_PAIR_STATIONARY,
-  O_PAIR_WS, O_PDL, O_POLL_LIMIT, O_SPIN_LIMIT, O_COUNT
+  O_PAIR_WS, O_LNQ_SMALL, O_PDL, O_POLL_LIMIT, O_SPIN_LIMIT, O_COUNT
 };
 struct OptDef { const char* name; int dflt; };
 const OptDef kOptDefs[O_COUNT] = {
@@ -86,7 +86,7 @@ const OptDef kOptDefs[O_COUNT] = {
     {"ARCQ_ACT_QUANT_V1", 0}, {"ARCQ_ACT_QUANT_V2", 0},   {"ARCQ_LN_PLAIN", 0},
     {"ARCQ_PAIR", 1},         {"ARCQ_PAIR_MIN_M", 1024},  {"ARCQ_PAIR_BN", 0},     {"ARCQ_PAIR_SA", 0},
     {"ARCQ_PAIR_KS", 0},      {"ARCQ_PAIR_NBB", 0},       {"ARCQ_PAIR_LUT", 0},    {"ARCQ_PAIR_PAIRS", 0},
-    {"ARCQ_PAIR_STATIONARY", -1}, {"ARCQ_PAIR_WS", 0}, {"ARCQ_PDL", 1},
+    {"ARCQ_PAIR_STATIONARY", -1}, {"ARCQ_PAIR_WS", 0}, {"ARCQ_LNQ_SMALL", 1}, {"ARCQ_PDL", 1},
     {"ARCQ_POLL_LIMIT", 1 << 21}, {"ARCQ_SPIN_LIMIT", 1 << 25},
 };
 int g_opt[O_COUNT];
@@ -1048,6 +1048,38 @@ int arcq_add_layernorm_act_quant(const void* x, const void* y, const float* gamm
   if (M == 0) return ARCQ_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int G = static_cast<int>(K / 64);
+  {
+    // Small inputs (the same bound below which the quantizer itself runs its eight-lanes-per-group form): the
+    // two-phase kernel whose results equal those of arcq_add_layernorm followed by arcq_act_quant bit for bit.
+    const bool small = M * G < static_cast<long long>(sm_count()) * 4 * arcq::kAq2Threads / 2 && opt(O_LNQ_SMALL) != 0;
+    if (small && (K == 192 || K == 384 || K == 768)) {
+      const __half *xs = static_cast<const __half*>(x), *ys = static_cast<const __half*>(y);
+      __half *so2 = static_cast<__half*>(sum_out), *ho2 = static_cast<__half*>(h_out), *xo2 = static_cast<__half*>(xhat);
+      const int lanes = static_cast<int>(K / 24), rows_tile = 4 * (32 / lanes);
+      const long long tiles2 = (M + rows_tile - 1) / rows_tile;
+      const long long cap2 = static_cast<long long>(sm_count()) * 8;
+      const unsigned grid2 = static_cast<unsigned>(tiles2 < cap2 ? tiles2 : cap2);
+#define ARCQ_LAUNCH_LNQ_ROWS(LN, B, HASY)                                                                            \
+  launch_pdl(arcq::add_layernorm_act_quant_rows_kernel<LN, B, HASY>, grid2, arcq::kLnqRowsThreads, 0, st, xs, ys, gamma, beta, eps,     \
+             static_cast<long long>(M), thresholds, codebook, so2, ho2, xo2)
+#define ARCQ_LNQ_ROWS_BITS(LN, HASY)                                                                                  \
+  do {                                                                                                                \
+    if (bits == 4) ARCQ_LAUNCH_LNQ_ROWS(LN, 4, HASY);                                                                  \
+    else if (bits == 3) ARCQ_LAUNCH_LNQ_ROWS(LN, 3, HASY);                                                             \
+    else ARCQ_LAUNCH_LNQ_ROWS(LN, 2, HASY);                                                                            \
+  } while (0)
+      if (y != nullptr) {
+        if (lanes == 8) ARCQ_LNQ_ROWS_BITS(8, true); else if (lanes == 16) ARCQ_LNQ_ROWS_BITS(16, true); else ARCQ_LNQ_ROWS_BITS(32, true);
+      } else {
+        if (lanes == 8) ARCQ_LNQ_ROWS_BITS(8, false); else if (lanes == 16) ARCQ_LNQ_ROWS_BITS(16, false); else ARCQ_LNQ_ROWS_BITS(32, false);
+      }
+#undef ARCQ_LNQ_ROWS_BITS
+#undef ARCQ_LAUNCH_LNQ_ROWS
+      cudaError_t e2 = cudaGetLastError();
+      if (e2 != cudaSuccess) return cuda_fail(e2, "add_layernorm_act_quant (rows) launch");
+      return ARCQ_OK;
+    }
+  }
   const int rows_per_tile = arcq::kLnqThreads / G;
   const long long tiles = (M + rows_per_tile - 1) / rows_per_tile;
   const long long cap = static_cast<long long>(sm_count()) * 4;

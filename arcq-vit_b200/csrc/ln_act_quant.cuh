@@ -17,6 +17,7 @@
 #include "ptx.cuh"
 #include "act_quant.cuh"
 #include "act_quant_v2.cuh"
+#include "add_layernorm.cuh"
 
 namespace arcq {
 
@@ -300,6 +301,116 @@ __global__ void __launch_bounds__(kLnqThreads, 4)
       }
     }
     __syncthreads();   // the staging rows are free for the next tile
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// The same operation for small inputs (a few hundred rows: batch 1-16 of a ViT), where the forward is a chain of
+// short launches and one launch fewer counts for more than instruction counts.  Blocks of twelve warps, two phases per
+// tile of 128 / LANES rows, through 6 KB of shared memory (the quantizer phase has three times as many lanes as the
+// LayerNorm phase has, so that it is a single pass and the block's latency is one LayerNorm plus one quantizer step):
+//   1. warps 0-3: residual add + LayerNorm with the lane layout and the arithmetic of add_layernorm_rows_kernel
+//      (the same device function), so s and h are bit-identical to that kernel's;
+//   2. all warps: the quantizer with the lane layout and the arithmetic of act_quant_kernel (eight lanes per group, IEEE
+//      division, chain sums in the reference's order), reading h from shared memory.
+// Its reconstruction therefore equals, bit for bit, what the two separate kernels produce, and a model may switch
+// between the merged and the separate form by batch size without changing a single output bit.
+constexpr int kLnqRowsThreads = 384;
+
+template <int LANES, int BITS, bool HAS_Y>
+__global__ void __launch_bounds__(kLnqRowsThreads) add_layernorm_act_quant_rows_kernel(const __half* __restrict__ x,
+                                                                          const __half* __restrict__ y,
+                                                                          const float* __restrict__ gamma,
+                                                                          const float* __restrict__ beta, float eps,
+                                                                          long long M,
+                                                                          const float* __restrict__ thresholds,
+                                                                          const float* __restrict__ codebook,
+                                                                          __half* __restrict__ sum_out,
+                                                                          __half* __restrict__ h_out,
+                                                                          __half* __restrict__ xhat) {
+  pdl_launch_dependents();
+  constexpr int L = 1 << BITS;
+  constexpr int K = LANES * 24, G = K / 64, kRowsPerWarp = 32 / LANES, kRows = 4 * kRowsPerWarp;   // rows per tile
+  constexpr int kSlots = kRows * G * 8;            // (group, lane-of-eight) pairs per tile: 384 for every width
+  static_assert(kSlots == kLnqRowsThreads, "the quantizer phase is one pass of the block");
+  __shared__ __align__(16) __half s_hid[kRows * K];
+  __shared__ float s_th[16];
+  __shared__ float s_cb[16];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, l = lane % LANES, sub = lane / LANES;
+  if (tid < 16) {
+    s_th[tid] = (tid < L - 1) ? thresholds[tid] : __int_as_float(0x7f800000);
+    s_cb[tid] = (tid < L) ? codebook[tid] : 0.0f;
+  }
+  float gg[3][8] = {}, bb[3][8] = {};
+  if (warp < 4) layernorm_lane_params<LANES>(gamma, beta, l, gg, bb);
+  __syncthreads();
+  pdl_wait();                // everything above is the layer's constants; x and y may be the previous kernel's output
+
+  const int l8 = lane & 7, octet_base = lane & ~7;
+  for (long long row0 = static_cast<long long>(blockIdx.x) * kRows; row0 < M; row0 += static_cast<long long>(gridDim.x) * kRows) {
+    // ---- phase 1 (warps 0-3): one row per LANES lanes
+    if (warp < 4) {
+      const int local = warp * kRowsPerWarp + sub;
+      const long long row = row0 + local;
+      const bool valid = row < M;
+      const long long rs = valid ? row : M - 1;
+      uint4 h[3];
+      layernorm_row<LANES>(x, HAS_Y ? y : nullptr, rs, row, valid, l, gg, bb, eps, sum_out, h);
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        reinterpret_cast<uint4*>(s_hid + local * K)[l + LANES * i] = h[i];
+        if (valid && h_out != nullptr) reinterpret_cast<uint4*>(h_out + row * K)[l + LANES * i] = h[i];
+      }
+    }
+    __syncthreads();
+    // ---- phase 2 (all warps): eight lanes per 64-group, lane l8 holds elements 8c + l8
+    {
+      const int grp = tid >> 3;                              // group of the tile
+      const int local = grp / G, g = grp - local * G;
+      const long long row = row0 + local;
+      const bool valid = row < M;
+      const __half* hg = s_hid + local * K + g * 64 + l8;
+      float v[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) v[c] = __half2float(hg[8 * c]);
+      float a0 = __fadd_rn(v[0], v[4]), a1 = __fadd_rn(v[1], v[5]);
+      float a2 = __fadd_rn(v[2], v[6]), a3 = __fadd_rn(v[3], v[7]);
+      float part = __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3);
+      const float mean = __fdiv_rn(octet_chain_sum(part, octet_base), 64.0f);
+      float r[8], q[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        r[c] = __fsub_rn(v[c], mean);
+        q[c] = __fmul_rn(r[c], r[c]);
+      }
+      a0 = __fadd_rn(q[0], q[4]); a1 = __fadd_rn(q[1], q[5]);
+      a2 = __fadd_rn(q[2], q[6]); a3 = __fadd_rn(q[3], q[7]);
+      part = __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3);
+      const float var = __fdiv_rn(octet_chain_sum(part, octet_base), 64.0f);
+      const float scale = __fsqrt_rn(__fadd_rn(var, 1.0e-6f));
+      float cv[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float t = __fdiv_rn(r[c], scale);
+        int code = 0;
+        if (BITS >= 4) code = (t > s_th[7]) ? 8 : 0;
+        if (BITS >= 3) code += (t > s_th[code + 3]) ? 4 : 0;
+        code += (t > s_th[code + 1]) ? 2 : 0;
+        code += (t > s_th[code]) ? 1 : 0;
+        cv[c] = s_cb[code];
+      }
+      a0 = __fadd_rn(cv[0], cv[4]); a1 = __fadd_rn(cv[1], cv[5]);
+      a2 = __fadd_rn(cv[2], cv[6]); a3 = __fadd_rn(cv[3], cv[7]);
+      part = __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3);
+      const float code_sum = octet_chain_sum(part, octet_base);
+      const float vm = __fdiv_rn(code_sum, 64.0f);
+      if (valid) {
+        __half* og = xhat + row * K + g * 64 + l8;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) og[8 * c] = __float2half_rn(__fadd_rn(mean, __fmul_rn(scale, __fsub_rn(cv[c], vm))));
+      }
+    }
+    __syncthreads();   // the tile's rows in shared memory are free for the next tile
   }
 }
 
