@@ -1040,7 +1040,8 @@ int arcq_add_layernorm_act_quant(const void* x, const void* y, const float* gamm
   if (group_size != 64) return fail(ARCQ_E_UNSUPPORTED, "group_size %d: only 64 is built", group_size);
   if (M < 0 || K <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape M=%lld K=%lld", (long long)M, (long long)K);
   if (K % 64 != 0) return fail(ARCQ_E_BAD_SHAPE, "K=%lld is not a multiple of the group size 64", (long long)K);
-  if (K / 64 > arcq::kLnqMaxG) return fail(ARCQ_E_TOO_LARGE, "rows longer than %d values are not built", 64 * arcq::kLnqMaxG);
+  if (K != 192 && K != 384 && K != 768)
+    return fail(ARCQ_E_UNSUPPORTED, "K=%lld: the merged kernel is built for rows of 192, 384 and 768 values", (long long)K);
   if (y == nullptr && sum_out != nullptr) return fail(ARCQ_E_BAD_ARG, "sum_out without y");
   if (!aligned(x, 16) || !aligned(xhat, 16) || (y != nullptr && !aligned(y, 16)) ||
       (sum_out != nullptr && !aligned(sum_out, 16)) || (h_out != nullptr && !aligned(h_out, 16)))
@@ -1052,7 +1053,7 @@ int arcq_add_layernorm_act_quant(const void* x, const void* y, const float* gamm
     // Small inputs (the same bound below which the quantizer itself runs its eight-lanes-per-group form): the
     // two-phase kernel whose results equal those of arcq_add_layernorm followed by arcq_act_quant bit for bit.
     const bool small = M * G < static_cast<long long>(sm_count()) * 4 * arcq::kAq2Threads / 2 && opt(O_LNQ_SMALL) != 0;
-    if (small && (K == 192 || K == 384 || K == 768)) {
+    if (small) {
       const __half *xs = static_cast<const __half*>(x), *ys = static_cast<const __half*>(y);
       __half *so2 = static_cast<__half*>(sum_out), *ho2 = static_cast<__half*>(h_out), *xo2 = static_cast<__half*>(xhat);
       const int lanes = static_cast<int>(K / 24), rows_tile = 4 * (32 / lanes);
@@ -1080,31 +1081,30 @@ int arcq_add_layernorm_act_quant(const void* x, const void* y, const float* gamm
       return ARCQ_OK;
     }
   }
-  const int rows_per_tile = arcq::kLnqThreads / G;
-  const long long tiles = (M + rows_per_tile - 1) / rows_per_tile;
+  const long long tiles = (M * G + arcq::kLnqThreads - 1) / arcq::kLnqThreads;
   const long long cap = static_cast<long long>(sm_count()) * 4;
   const unsigned grid = static_cast<unsigned>(tiles < cap ? tiles : cap);
-  const size_t smem = arcq::lnq_smem_bytes(G);
+  const size_t smem = arcq::lnq_smem_bytes();
   const __half *xh = static_cast<const __half*>(x), *yh = static_cast<const __half*>(y);
   __half *so = static_cast<__half*>(sum_out), *ho = static_cast<__half*>(h_out), *xo = static_cast<__half*>(xhat);
-#define ARCQ_LAUNCH_LNQ(B, HASY)                                                                                       \
-  do {                                                                                                                 \
-    static thread_local int done_dev = -1;                                                                             \
-    int dev = 0;                                                                                                       \
-    cudaGetDevice(&dev);                                                                                               \
-    if (done_dev != dev) {                                                                                             \
-      cudaFuncSetAttribute(arcq::add_layernorm_act_quant_kernel<B, HASY>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                           static_cast<int>(arcq::lnq_smem_bytes(arcq::kLnqMaxG)));                                    \
-      done_dev = dev;                                                                                                  \
-    }                                                                                                                  \
-    launch_pdl(arcq::add_layernorm_act_quant_kernel<B, HASY>, grid, arcq::kLnqThreads, smem, st, xh, yh, gamma, beta,  \
-               eps, static_cast<long long>(M), G, thresholds, codebook, so, ho, xo);                                   \
+#define ARCQ_LAUNCH_LNQ(LN, B, HASY)                                                                                   \
+  launch_pdl(arcq::add_layernorm_act_quant_kernel<LN, B, HASY>, grid, arcq::kLnqThreads, smem, st, xh, yh, gamma, beta, \
+             eps, static_cast<long long>(M), thresholds, codebook, so, ho, xo)
+#define ARCQ_LNQ_BITS(LN, HASY)                                                                                         \
+  do {                                                                                                                  \
+    if (bits == 4) ARCQ_LAUNCH_LNQ(LN, 4, HASY);                                                                         \
+    else if (bits == 3) ARCQ_LAUNCH_LNQ(LN, 3, HASY);                                                                    \
+    else ARCQ_LAUNCH_LNQ(LN, 2, HASY);                                                                                   \
   } while (0)
-  if (y != nullptr) {
-    if (bits == 4) ARCQ_LAUNCH_LNQ(4, true); else if (bits == 3) ARCQ_LAUNCH_LNQ(3, true); else ARCQ_LAUNCH_LNQ(2, true);
-  } else {
-    if (bits == 4) ARCQ_LAUNCH_LNQ(4, false); else if (bits == 3) ARCQ_LAUNCH_LNQ(3, false); else ARCQ_LAUNCH_LNQ(2, false);
+  {
+    const int lanes = static_cast<int>(K / 24);
+    if (y != nullptr) {
+      if (lanes == 8) ARCQ_LNQ_BITS(8, true); else if (lanes == 16) ARCQ_LNQ_BITS(16, true); else ARCQ_LNQ_BITS(32, true);
+    } else {
+      if (lanes == 8) ARCQ_LNQ_BITS(8, false); else if (lanes == 16) ARCQ_LNQ_BITS(16, false); else ARCQ_LNQ_BITS(32, false);
+    }
   }
+#undef ARCQ_LNQ_BITS
 #undef ARCQ_LAUNCH_LNQ
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "add_layernorm_act_quant launch");

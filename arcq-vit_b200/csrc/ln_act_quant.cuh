@@ -1,17 +1,21 @@
-// Residual add + LayerNorm + activation quantizer in one pass over fp16 rows: the glue in front of the first
+// Residual add + LayerNorm + activation quantizer in one kernel over fp16 rows: the glue in front of the first
 // packed linear of a sub-block (norm1 -> qkv, norm2 -> fc1) merged with that linear's input quantizer.
 //   s    = fp16(x + y)                                    (written out when y is given: the residual stream)
 //   h    = fp16((s - mean(s)) * rsqrt(var(s) + eps) * gamma + beta)     (never written, unless asked for)
 //   xhat = fp16(reconstruction of the ARCQ quantization of h in groups of 64)
-// The separate kernels write h and read it back; here it stays in registers.
+// The separate kernels write h and read it back; here it goes through shared memory.
 //
-// Layout: one thread per 64-value group, as in the staged quantizer (act_quant_v2.cuh, which documents the
-// summation order, the division-free exact threshold test and the first-guess grid used below).  A tile is
-// R whole rows (R * K/64 <= 128 groups); x and y tiles are staged through shared memory with 16-byte
-// cp.async, the LayerNorm statistics of a row are the sums of its K/64 threads' partial sums, combined
-// through shared memory in a fixed order, so a row's result does not depend on the tile it falls in.
-// The quantizer part takes the fp16-rounded h, i.e. exactly what the separate quantizer kernel would read:
-// given the same h both produce the same bits.
+// Two phases per tile, each in the thread layout that suits it, and each with the arithmetic of the kernel it
+// replaces, so that the results are bit-identical to arcq_add_layernorm followed by arcq_act_quant:
+//   1. LayerNorm with the lane layout of add_layernorm_rows_kernel (LANES lanes per row, 16-byte accesses, the same
+//      device function), writing h into padded group rows of shared memory;
+//   2. the quantizer of act_quant_v2_kernel: one thread per 64-group reads its row, classifies with the exact
+//      division-free test and the first-guess grid (that file documents both), writes the reconstruction back over
+//      the row, and the block copies the rows out coalesced.
+// A tile is 128 consecutive groups (the quantizer's unit), whatever the row length: the LayerNorm phase computes
+// every row the tile touches (a row shared with the neighbouring tile is normalised by both; 1 row in 22 at
+// K = 384) and keeps the groups that are the tile's.  Rows are owned (s and h written) by the tile that holds
+// their first group.
 #pragma once
 #include <cuda_fp16.h>
 #include "ptx.cuh"
@@ -23,44 +27,36 @@ namespace arcq {
 
 constexpr int kLnqThreads = 128;
 constexpr int kLnqPitch = 144;      // bytes between staged group rows (128 data bytes, conflict-free pitch)
-constexpr int kLnqMaxG = 16;        // rows of up to 1024 values
 
-__host__ __device__ constexpr size_t lnq_smem_bytes(int G) {
-  return 2 * kLnqThreads * kLnqPitch            // x / residual-sum rows, y / reconstruction rows
+__host__ __device__ constexpr size_t lnq_smem_bytes() {
+  return kLnqThreads * kLnqPitch                // h, then reconstruction rows
          + 16 * kLnqThreads * 4                 // per-thread limit columns
-         + 2 * kLnqThreads * 4                  // partial sums, partial sums of squares
-         + static_cast<size_t>(G) * 65 * 8      // (gamma, beta) pairs, one padded row of 65 per group
          + 4 * 16 * 4 + kAq2Cells * 4 + 16;     // thresholds, half-gaps, codebook, grid positions, first guesses
 }
 
-template <int BITS, bool HAS_Y>
+template <int LANES, int BITS, bool HAS_Y>
 __global__ void __launch_bounds__(kLnqThreads, 4)
     add_layernorm_act_quant_kernel(const __half* __restrict__ x, const __half* __restrict__ y,
                                    const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
-                                   long long M, int G, const float* __restrict__ thresholds,
+                                   long long M, const float* __restrict__ thresholds,
                                    const float* __restrict__ codebook, __half* __restrict__ sum_out,
                                    __half* __restrict__ h_out, __half* __restrict__ xhat) {
   pdl_launch_dependents();   // the next kernel of the stream may start its set-up
 
   constexpr int L = 1 << BITS;
+  constexpr int K = LANES * 24, G = K / 64, kRowsPerWarp = 32 / LANES, kRowsPerPass = 4 * kRowsPerWarp;
+  constexpr int kMaxRows = kLnqThreads / G + 2;                       // rows a tile of 128 groups can touch
+  constexpr int kPasses = (kMaxRows + kRowsPerPass - 1) / kRowsPerPass;
   constexpr int kTableStride = kLnqThreads;
   extern __shared__ __align__(16) uint8_t lnq_smem[];
-  uint8_t* const s_a = lnq_smem;                                          // x, then s = x + y
-  uint8_t* const s_b = s_a + kLnqThreads * kLnqPitch;                     // y, then the reconstruction
-  float* const s_table = reinterpret_cast<float*>(s_b + kLnqThreads * kLnqPitch);   // [16][128]
-  float* const s_p1 = s_table + 16 * kTableStride;                        // [128]
-  float* const s_p2 = s_p1 + kLnqThreads;                                 // [128]
-  float2* const s_gb = reinterpret_cast<float2*>(s_p2 + kLnqThreads);     // [G][65]
-  float* const s_th = reinterpret_cast<float*>(s_gb + G * 65);            // [16]
+  uint8_t* const s_rows = lnq_smem;                                                   // [128] group rows
+  float* const s_table = reinterpret_cast<float*>(s_rows + kLnqThreads * kLnqPitch);  // [16][128]
+  float* const s_th = s_table + 16 * kTableStride;                                    // [16]
   float* const s_h = s_th + 16;
   float* const s_cb = s_h + 16;
   float* const s_pos = s_cb + 16;
-  int* const s_guess = reinterpret_cast<int*>(s_pos + 16);                // [kAq2Cells]
-  const int tid = threadIdx.x;
-  const int K = G * 64;
-  const int R = kLnqThreads / G;            // rows per tile
-  const int active = R * G;                 // threads that own a group
-  const int my_row = tid / G, my_g = tid - my_row * G;
+  int* const s_guess = reinterpret_cast<int*>(s_pos + 16);                            // [kAq2Cells]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, l = lane % LANES, sub = lane / LANES;
 
   // ---- per-block set-up (reads only this layer's constants, so it runs before the wait below)
   int my_exact = 1;
@@ -81,7 +77,6 @@ __global__ void __launch_bounds__(kLnqThreads, 4)
     s_h[tid] = h;
     s_cb[tid] = tid < L ? codebook[tid] : 0.0f;
   }
-  for (int i = tid; i < K; i += kLnqThreads) s_gb[(i >> 6) * 65 + (i & 63)] = make_float2(__ldg(gamma + i), __ldg(beta + i));
   const bool exact_r = __syncthreads_and(my_exact) != 0;
   float grid_scale = 0.0f, grid_off = 0.0f;
   bool use_guess = false;
@@ -109,120 +104,52 @@ __global__ void __launch_bounds__(kLnqThreads, 4)
   const char* const col = reinterpret_cast<const char*>(my_table);
   constexpr int kStep = kTableStride * 4;
   static_assert(kStep == 512, "the code extraction below assumes a 512-byte table step");
-  const float2* const my_gb = s_gb + my_g * 65;
-  const float inv_k = 1.0f / static_cast<float>(K);
+  uint8_t* const my_row = s_rows + tid * kLnqPitch;
 
   pdl_wait();                // x and y may be the previous kernels' outputs
 
-  const long long tiles = (M + R - 1) / R;
+  const long long total_groups = M * G;
+  const long long tiles = (total_groups + kLnqThreads - 1) / kLnqThreads;
   for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-    const long long row0 = tile * R;
-    const int rows = static_cast<int>(min(static_cast<long long>(R), M - row0));
-    const int ngroups = rows * G;
-    // ---- stage the tile: rows are contiguous in memory, so the tile is one run of 128-byte group rows
+    const long long gi0 = tile * kLnqThreads;
+    const int ngroups = static_cast<int>(min(static_cast<long long>(kLnqThreads), total_groups - gi0));
+    const long long r_first = gi0 / G;
+    // ---- phase 1: LayerNorm of every row the tile touches, LANES lanes per row
     {
-      const int nchunks = ngroups * 8;
-      const uint8_t* xs = reinterpret_cast<const uint8_t*>(x + row0 * K);
-      const uint8_t* ys = HAS_Y ? reinterpret_cast<const uint8_t*>(y + row0 * K) : nullptr;
-      const uint32_t da = smem_u32(s_a), db = smem_u32(s_b);
+      float gg[3][8], bb[3][8];
+      layernorm_lane_params<LANES>(gamma, beta, l, gg, bb);
+#pragma unroll 1
+      for (int pass = 0; pass < kPasses; ++pass) {
+        const long long row = r_first + pass * kRowsPerPass + warp * kRowsPerWarp + sub;
+        const long long lg0 = row * G - gi0;                       // tile-local index of the row's first group
+        const bool in_tile = row < M && lg0 < ngroups;             // the row has groups in this tile
+        const bool owned = in_tile && lg0 >= 0;                    // ... and its first group is one of them
+        const long long rs = row < M ? row : M - 1;                // idle sub-warps shadow the last row
+        uint4 h[3];
+        layernorm_row<LANES>(x, HAS_Y ? y : nullptr, rs, row, owned, l, gg, bb, eps, sum_out, h);
+        if (in_tile) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int q = tid + kLnqThreads * i;
-        if (q < nchunks) {
-          cp_async16(da + (q >> 3) * kLnqPitch + (q & 7) * 16, xs + q * 16);
-          if (HAS_Y) cp_async16(db + (q >> 3) * kLnqPitch + (q & 7) * 16, ys + q * 16);
+          for (int i = 0; i < 3; ++i) {
+            const int ch = l + LANES * i;                          // 16-byte chunk of the row: group ch / 8, part ch % 8
+            const long long lg = lg0 + (ch >> 3);
+            if (lg >= 0 && lg < ngroups)
+              *reinterpret_cast<uint4*>(s_rows + lg * kLnqPitch + (ch & 7) * 16) = h[i];
+            if (owned && h_out != nullptr) reinterpret_cast<uint4*>(h_out + row * K)[ch] = h[i];
+          }
         }
       }
-      cp_async_commit();
-      cp_async_wait<0>();
     }
     __syncthreads();
 
+    // ---- phase 2: the activation quantizer on h, one thread per group (same steps as act_quant_v2_kernel)
     const bool valid = tid < ngroups;
-    uint8_t* const row_a = s_a + tid * kLnqPitch;
-    uint8_t* const row_b = s_b + tid * kLnqPitch;
     float v[64];
     if (valid) {
-      aq2_load_row<__half>(row_a, v);
-      if (HAS_Y) {
-        // s = fp16(x + y): the sum a separate add would store, written back over the staged x row
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 u = *reinterpret_cast<const uint4*>(row_b + 16 * c);
-          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-          uint32_t o[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-            const __half2 s2 = __floats2half2_rn(v[8 * c + 2 * j] + f.x, v[8 * c + 2 * j + 1] + f.y);
-            o[j] = *reinterpret_cast<const uint32_t*>(&s2);
-            const float2 fs = __half22float2(s2);
-            v[8 * c + 2 * j] = fs.x;
-            v[8 * c + 2 * j + 1] = fs.y;
-          }
-          *reinterpret_cast<uint4*>(row_a + 16 * c) = make_uint4(o[0], o[1], o[2], o[3]);
-        }
-      }
+      aq2_load_row<__half>(my_row, v);
     } else {
 #pragma unroll
       for (int j = 0; j < 64; ++j) v[j] = 0.0f;
     }
-
-    // ---- LayerNorm statistics of the row: two passes, partial sums of the row's G threads added in group order
-    {
-      float p[8];
-#pragma unroll
-      for (int l = 0; l < 8; ++l) p[l] = ((v[l] + v[8 + l]) + (v[16 + l] + v[24 + l])) + ((v[32 + l] + v[40 + l]) + (v[48 + l] + v[56 + l]));
-      s_p1[tid] = ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));
-    }
-    __syncthreads();
-    float mean_ln = 0.0f;
-    if (valid) {
-      const float* pr = s_p1 + my_row * G;
-      for (int g = 0; g < G; ++g) mean_ln += pr[g];
-      mean_ln *= inv_k;
-    }
-    {
-      float p[8];
-#pragma unroll
-      for (int l = 0; l < 8; ++l) {
-        p[l] = 0.0f;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const float d = v[8 * c + l] - mean_ln;
-          p[l] = fmaf(d, d, p[l]);
-        }
-      }
-      s_p2[tid] = ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));
-    }
-    __syncthreads();
-    if (valid) {
-      float sq = 0.0f;
-      const float* pr = s_p2 + my_row * G;
-      for (int g = 0; g < G; ++g) sq += pr[g];
-      const float rstd = rsqrtf(sq * inv_k + eps);
-      // h in fp16, as the LayerNorm kernel stores it; from here on v holds what the quantizer would read
-#pragma unroll
-      for (int j = 0; j < 64; j += 2) {
-        const float2 gb0 = my_gb[j], gb1 = my_gb[j + 1];
-        const __half2 h2 = __floats2half2_rn((v[j] - mean_ln) * rstd * gb0.x + gb0.y, (v[j + 1] - mean_ln) * rstd * gb1.x + gb1.y);
-        const float2 f = __half22float2(h2);
-        v[j] = f.x;
-        v[j + 1] = f.y;
-      }
-      if (h_out != nullptr) {
-        __half* ho = h_out + (row0 + my_row) * K + my_g * 64;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint32_t o[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) o[j] = aq2_pack2<__half>(v[8 * c + 2 * j], v[8 * c + 2 * j + 1]);
-          *reinterpret_cast<uint4*>(ho + 8 * c) = make_uint4(o[0], o[1], o[2], o[3]);
-        }
-      }
-    }
-
-    // ---- the activation quantizer on h (same steps as act_quant_v2_kernel)
     const float mean = __fdiv_rn(sum64_ref_order(v), 64.0f);
     float var;
     {
@@ -281,26 +208,22 @@ __global__ void __launch_bounds__(kLnqThreads, 4)
           o[j] = aq2_pack2<__half>(__fadd_rn(mean, __fmul_rn(scale, __fsub_rn(v[e], vm))),
                                    __fadd_rn(mean, __fmul_rn(scale, __fsub_rn(v[e + 1], vm))));
         }
-        *reinterpret_cast<uint4*>(row_b + 16 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(my_row + 16 * c) = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
     __syncthreads();
-    // ---- coalesced copy-out of the residual stream and the reconstruction
+    // ---- coalesced copy-out of the reconstruction (groups are contiguous in memory)
     {
       const int nchunks = ngroups * 8;
-      uint8_t* so = (HAS_Y && sum_out != nullptr) ? reinterpret_cast<uint8_t*>(sum_out + row0 * K) : nullptr;
-      uint8_t* xo = reinterpret_cast<uint8_t*>(xhat + row0 * K);
+      uint8_t* xo = reinterpret_cast<uint8_t*>(xhat) + gi0 * 128;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int q = tid + kLnqThreads * i;
-        if (q < nchunks) {
-          if (HAS_Y && so != nullptr)
-            *reinterpret_cast<uint4*>(so + q * 16) = *reinterpret_cast<const uint4*>(s_a + (q >> 3) * kLnqPitch + (q & 7) * 16);
-          *reinterpret_cast<uint4*>(xo + q * 16) = *reinterpret_cast<const uint4*>(s_b + (q >> 3) * kLnqPitch + (q & 7) * 16);
-        }
+        if (q < nchunks)
+          *reinterpret_cast<uint4*>(xo + q * 16) = *reinterpret_cast<const uint4*>(s_rows + (q >> 3) * kLnqPitch + (q & 7) * 16);
       }
     }
-    __syncthreads();   // the staging rows are free for the next tile
+    __syncthreads();   // the rows are free for the next tile
   }
 }
 

@@ -232,6 +232,11 @@ def add_layernorm_quant(x: torch.Tensor, y, norm: torch.nn.LayerNorm, thresholds
     x2 = _dev(x.reshape(-1, K), "x", torch.float16)
     y2 = None if y is None else _dev(y.reshape(-1, K), "y", torch.float16)
     thresholds, codebook = _dev(thresholds, "thresholds", torch.float32), _dev(codebook, "codebook", torch.float32)
+    if K not in (192, 384, 768):
+        # widths the merged kernel is not built for: the two kernels it stands for (same results)
+        s, h = add_layernorm(x, y, norm)
+        xh = quantize_activation_dequant(h.reshape(-1, K), thresholds, codebook, bits, group_size, torch.float16)
+        return (s, xh.reshape(shape), h) if want_h else (s, xh.reshape(shape))
     g32, b32 = _norm_params_f32(norm, x2.device)
     xhat = torch.empty_like(x2)
     s_out = torch.empty_like(x2) if y2 is not None else None

@@ -101,14 +101,10 @@ class PatchEmbed(nn.Module):
 
 
 class VisionTransformer(nn.Module):
-    # The LayerNorm in front of qkv / fc1 can also run that layer's activation quantizer (one kernel instead of two,
-    # the LayerNorm output never written).
-    #   "auto": only for small inputs (fewer than 37 888 groups: batch <= 32 of DeiT-S), where the forward is a chain of
-    #           short launches; the small-input kernel gives the same bits as the two separate kernels.
-    #   "1":    always.  At batch 64 both kernels are bound by instruction issue, not by memory, so the merged kernel
-    #           costs the sum of the two (16.1 us against 17.8 us for [12608, 384]) and the whole DeiT-S forward
-    #           measured 4 % slower with it: two short kernels overlap better with their neighbours than one long one.
-    #   "0":    never.
+    # The LayerNorm in front of qkv / fc1 also runs that layer's activation quantizer (one kernel instead of two, the
+    # LayerNorm output never leaves the SM): "auto" / "1" wherever the merged kernel is built (rows of 192, 384 or 768
+    # values), "0" never.  The merged kernel gives the same bits as the two separate kernels, so the switch changes
+    # timing only (DeiT-S batch 64: 1.96 -> 1.85 ms; batch 1: 0.525 -> 0.509 ms).
     fuse_norm_quant = os.environ.get("ARCQ_LN_QUANT", "auto")
 
     def __init__(self, dim: int, heads: int, depth: int, num_classes: int = 1000, img_size: int = 224,
@@ -142,8 +138,8 @@ class VisionTransformer(nn.Module):
             linear also runs that linear's activation quantizer when the layer can take the result."""
             mode = self.fuse_norm_quant
             mode = "1" if mode is True else "0" if mode is False else str(mode)
-            rows, width = x.numel() // x.shape[-1], x.shape[-1]
-            fuse = mode == "1" or (mode == "auto" and width in (192, 384, 768) and rows * (width // 64) < 37888)
+            width = x.shape[-1]
+            fuse = mode in ("1", "auto") and width in (192, 384, 768)
             if fuse and isinstance(lin, ARCQPackedLinearOnTheFly) and lin.takes_reconstructed_input():
                 s, xh = ops.add_layernorm_quant(x, y, norm, lin.activation_thresholds, lin.activation_codebook,
                                                 lin.bits, lin.group_size)

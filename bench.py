@@ -299,6 +299,16 @@ def kernel_rooflines(pkg, a, dev, pk):
     return out
 
 
+def launches_per_forward(pkg, a, n_lin: int, batch: int) -> int:
+    """This repository's kernel launches in one forward of the benchmark model (torch / cuDNN kernels not counted)."""
+    dim, _, depth = pkg.DEIT_CONFIGS[a.model]
+    staged = batch * TOKENS >= pkg.WeightStager.min_rows and pkg.ARCQPackedLinearOnTheFly.weight_form in ("auto", "staged")
+    merged = str(pkg.VisionTransformer.fuse_norm_quant) in ("auto", "1", "True") and dim in (192, 384, 768)
+    norms = 2 * depth + 1
+    quantizers = n_lin - (2 * depth if merged else 0)
+    return n_lin * (2 if staged else 1) + norms + quantizers
+
+
 def _time_forward(runner, x, warm: int, iters: int) -> float:
     """Milliseconds per call of ``runner(x)`` (CUDA events on the current stream)."""
     with torch.no_grad():
@@ -524,10 +534,10 @@ def run_gpu_arm(a):
             "e2e": {"value": global_batch * a.steps / (ms_e2e / 1e3), "unit": "images/s",
                     "h2d_bytes_per_step": host_batches[0].numel() * 2, "d2h_bytes_per_step": host_logits.numel() * 2,
                     "ms_per_step": ms_e2e / a.steps},
-            # per forward: one quantizer and one GEMM per packed linear, one add+LayerNorm kernel per norm
-            # (a third per linear at batch sizes that take the staged weight route: the weight unpack)
-            "gpu_launches": ((3 if B * TOKENS >= pkg.WeightStager.min_rows and pkg.ARCQPackedLinearOnTheFly.weight_form == "auto"
-                              else 2) * n_lin + 2 * pkg.DEIT_CONFIGS[a.model][2] + 1) * a.steps,
+            # per forward: one GEMM and (staged weight route) one weight unpack per packed linear; one add+LayerNorm
+            # kernel per norm, which also runs the quantizer of qkv / fc1 when the merged kernel is on; one
+            # quantizer per remaining packed linear
+            "gpu_launches": launches_per_forward(pkg, a, n_lin, B) * a.steps,
             "clocks": clocks, "device_status": status,
         }
         if gather_check is not None:

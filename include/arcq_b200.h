@@ -208,8 +208,9 @@ int arcq_add_layernorm(const void* x, const void* y, const float* gamma, const f
  * output (timm Block.forward: norm1 -> attn.qkv, norm2 -> mlp.fc1), in one kernel:
  *   s = fp16(x + y) -> sum_out (y and sum_out may be NULL together);  h = fp16(LayerNorm(s));
  *   xhat = what arcq_act_quant(h, ..., xhat_dtype fp16) reconstructs.
- * h is not written unless h_out is given (for checking: arcq_act_quant on that h gives the same xhat bits).
- * fp16 rows of K values, K a multiple of 64 and at most 1024; group_size 64.
+ * h is not written unless h_out is given.  s, h and xhat are bit-identical to arcq_add_layernorm followed by
+ * arcq_act_quant (the kernel shares their arithmetic), at every size.
+ * fp16 rows of K = 192, 384 or 768 values (ARCQ_E_UNSUPPORTED otherwise); group_size 64.
  */
 int arcq_add_layernorm_act_quant(const void* x, const void* y, const float* gamma, const float* beta, float eps,
                                  int64_t M, int64_t K, const float* thresholds, const float* codebook, int bits,
