@@ -102,27 +102,35 @@ __global__ void __launch_bounds__(256) add_layernorm_kernel(const __half* __rest
 // as the lane's three packed chunks.  `rs` is the row to read (idle sub-warps shadow the last row), `row` the row
 // to store (only if `valid`).  Shared by the LayerNorm kernel below and by the small-batch LayerNorm + quantizer
 // kernel (ln_act_quant.cuh), so that the two produce the same bits.
+// The lane's three chunks of row `rs` of x (and of y, if given).
 template <int LANES>
-__device__ __forceinline__ void layernorm_row(const __half* __restrict__ x, const __half* __restrict__ y, long long rs,
-                                              long long row, bool valid, int l, const float (&gg)[3][8],
-                                              const float (&bb)[3][8], float eps, __half* __restrict__ sum_out,
-                                              uint4 (&h)[3]) {
+__device__ __forceinline__ void layernorm_row_load(const __half* __restrict__ x, const __half* __restrict__ y,
+                                                   long long rs, int l, uint4 (&a)[3], uint4 (&b)[3]) {
   constexpr int K = LANES * 24;
   const uint4* xr = reinterpret_cast<const uint4*>(x + rs * K);
-  const uint4* yr = (y != nullptr) ? reinterpret_cast<const uint4*>(y + rs * K) : nullptr;
-  uint4 a[3], b[3];
 #pragma unroll
   for (int i = 0; i < 3; ++i) a[i] = __ldg(xr + l + LANES * i);
-  if (yr != nullptr) {
+  if (y != nullptr) {
+    const uint4* yr = reinterpret_cast<const uint4*>(y + rs * K);
 #pragma unroll
     for (int i = 0; i < 3; ++i) b[i] = __ldg(yr + l + LANES * i);
   }
+}
+
+// The arithmetic of one row on chunks already loaded (`has_y`: b holds the residual branch).
+template <int LANES>
+__device__ __forceinline__ void layernorm_row_compute(const uint4 (&a)[3], const uint4 (&b)[3], bool has_y,
+                                                      long long row, bool valid, int l, const float (&gg)[3][8],
+                                                      const float (&bb)[3][8], float eps,
+                                                      __half* __restrict__ sum_out, uint4 (&h)[3]) {
+  constexpr int K = LANES * 24;
+  const bool yr = has_y;
   float v[3][8];
   float sum = 0.0f;
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
     const __half2* ah = reinterpret_cast<const __half2*>(&a[i]);
-    if (yr != nullptr) {
+    if (yr) {
       const __half2* bh = reinterpret_cast<const __half2*>(&b[i]);
       uint4 so;
       __half2* sh = reinterpret_cast<__half2*>(&so);
@@ -169,6 +177,16 @@ __device__ __forceinline__ void layernorm_row(const __half* __restrict__ x, cons
       oh[j] = __floats2half2_rn((v[i][2 * j] - mean) * rstd * gg[i][2 * j] + bb[i][2 * j],
                                 (v[i][2 * j + 1] - mean) * rstd * gg[i][2 * j + 1] + bb[i][2 * j + 1]);
   }
+}
+
+template <int LANES>
+__device__ __forceinline__ void layernorm_row(const __half* __restrict__ x, const __half* __restrict__ y, long long rs,
+                                              long long row, bool valid, int l, const float (&gg)[3][8],
+                                              const float (&bb)[3][8], float eps, __half* __restrict__ sum_out,
+                                              uint4 (&h)[3]) {
+  uint4 a[3], b[3];
+  layernorm_row_load<LANES>(x, y, rs, l, a, b);
+  layernorm_row_compute<LANES>(a, b, y != nullptr, row, valid, l, gg, bb, eps, sum_out, h);
 }
 
 // gamma and beta of the lane's three chunks
