@@ -11,9 +11,11 @@ contract of the reference's packed layers:
   methods/fair_qat_framework/fair_qat/arcq_packed_on_the_fly.py:93-169.  Built from buffers;
   ``forward`` returns fp16 ("half chain").
 
-Both forwards are the same two launches behind the C ABI: the activation quantizer
-(packed codes + per-group statistics) and the fused packed GEMM (tcgen05).  There is no
-Triton, no cuBLAS and no CPU path; without the built library the forward raises.
+Both forwards are launches behind the C ABI: the activation quantizer (packed codes + per-group
+statistics, or the fp16 reconstruction) and a tcgen05 GEMM -- with the weight rebuilt inside the
+kernel, or unpacked by a third launch on a side stream while the previous layer runs (``staging.py``);
+the routes give the same bits.  There is no Triton, no cuBLAS and no CPU path; without the built
+library the forward raises.
 
 Added on this side of the boundary (the reference never loads its own packed
 checkpoints back): ``ARCQPackedLinear.from_state_dict`` / ``from_buffers``.
