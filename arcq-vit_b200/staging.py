@@ -10,6 +10,10 @@ Nothing but the packed codes is kept between forwards; the scratch is two matric
 The order of the layers is their registration order in the model (timm's and this package's ViT register
 qkv, proj, fc1, fc2 block by block, which is the order they run in).  A layer that is called out of that
 order, or on its own, simply unpacks its weight when it is called.
+
+A stager belongs to one model and keeps per-forward state (which layer each scratch matrix holds, the events that
+order the two streams): one forward of that model at a time.  Concurrent forwards of the same model from several host
+threads need one model copy (and stager) per thread; the packed buffers can be shared.
 """
 from __future__ import annotations
 
