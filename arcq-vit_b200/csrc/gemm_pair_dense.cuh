@@ -42,7 +42,9 @@ struct PairDenseParams {
 constexpr int kPairDenseThreads = (2 + kPairEpiWarps) * 32;
 // Staging blocks (2 KB: 32 rows x 64 bytes) per epilogue warp; a block can be rewritten once the TMA store that
 // reads it has done so.  Four blocks instead of two measured slower on every DeiT-S shape (qkv 13.6 -> 15.5 us,
-// fc2 17.5 -> 22.3 us): the 32 KB they take away from the operand stages cost more than deeper stores gain.
+// fc2 17.5 -> 22.3 us): the 32 KB they take away from the operand stages cost more than deeper stores gain.  One
+// block (16 KB more for the stages) helped only the layer with few stores per flop (fc2 17.5 -> 17.0 us) and cost
+// the store-heavy ones (qkv 13.8 -> 14.5 us, fc1 16.5 -> 16.9 us).
 #ifndef ARCQ_DENSE_STAGE_BLOCKS
 #define ARCQ_DENSE_STAGE_BLOCKS 2
 #endif
