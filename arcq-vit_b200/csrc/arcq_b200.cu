@@ -23,6 +23,7 @@
 #include "add_layernorm.cuh"
 #include "ln_act_quant.cuh"
 #include "attention.cuh"
+#include "patch_embed.cuh"
 #include <cudaTypedefs.h>
 
 namespace {
@@ -1162,6 +1163,41 @@ int arcq_attention_act_quant(const void* qkv, int64_t B, int64_t T, int64_t H, i
   if (bits < 2 || bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", bits);
   if (group_size != 64) return fail(ARCQ_E_UNSUPPORTED, "group_size %d: only 64 is built", group_size);
   return launch_attention(qkv, B, T, H, head_dim, thresholds, codebook, bits, xhat, stream);
+}
+
+int arcq_patchify(const void* images, int64_t B, int64_t C, int64_t H, int64_t W, int patch, void* rows, void* stream) {
+  if (images == nullptr || rows == nullptr) return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (B < 0 || C <= 0 || H <= 0 || W <= 0 || patch <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape");
+  if (patch % 8 != 0 || H % patch != 0 || W % patch != 0)
+    return fail(ARCQ_E_UNSUPPORTED, "patch %d: must be a multiple of 8 that divides H=%lld and W=%lld", patch, (long long)H, (long long)W);
+  if (B * C * H * W > 0x7fffffffffLL) return fail(ARCQ_E_TOO_LARGE, "image batch too large");
+  if (!aligned(images, 16) || !aligned(rows, 16)) return fail(ARCQ_E_ALIGN, "images and rows must be 16-byte aligned");
+  if (B == 0) return ARCQ_OK;
+  const long long chunks = B * C * H * W / 8;
+  launch_pdl(arcq::patchify_kernel, grid_for(chunks, 256, 8), 256, 0, static_cast<cudaStream_t>(stream),
+             static_cast<const __half*>(images), static_cast<int>(B), static_cast<int>(C), static_cast<int>(H),
+             static_cast<int>(W), patch, static_cast<__half*>(rows));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "patchify launch");
+  return ARCQ_OK;
+}
+
+int arcq_assemble_tokens(const void* patches, const void* cls_token, const void* pos_embed, int64_t B, int64_t T, int64_t D,
+                         void* tokens, void* stream) {
+  if (patches == nullptr || cls_token == nullptr || pos_embed == nullptr || tokens == nullptr)
+    return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (B < 0 || T <= 0 || D <= 0 || D % 8 != 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape B=%lld T=%lld D=%lld", (long long)B, (long long)T, (long long)D);
+  if (!aligned(patches, 16) || !aligned(cls_token, 16) || !aligned(pos_embed, 16) || !aligned(tokens, 16))
+    return fail(ARCQ_E_ALIGN, "all buffers must be 16-byte aligned");
+  if (B == 0) return ARCQ_OK;
+  const long long chunks = B * (T + 1) * (D / 8);
+  launch_pdl(arcq::assemble_tokens_kernel, grid_for(chunks, 256, 8), 256, 0, static_cast<cudaStream_t>(stream),
+             static_cast<const __half*>(patches), static_cast<const __half*>(cls_token),
+             static_cast<const __half*>(pos_embed), static_cast<int>(B), static_cast<int>(T), static_cast<int>(D),
+             static_cast<__half*>(tokens));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "assemble_tokens launch");
+  return ARCQ_OK;
 }
 
 int arcq_unpack_codes(const uint8_t* packed, int64_t rows, int64_t length, int bits, uint8_t* codes_out, void* stream) {

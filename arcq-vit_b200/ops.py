@@ -275,6 +275,33 @@ def attention(qkv: torch.Tensor, batch: int, tokens: int, heads: int, thresholds
     return out
 
 
+def patchify(images: torch.Tensor, patch: int) -> torch.Tensor:
+    """fp16 images [B, C, H, W] -> [B, (H/patch)*(W/patch), C*patch*patch]: row (gy, gx), column (c, py, px), i.e.
+    ``images.reshape(B, C, gh, p, gw, p).permute(0, 2, 4, 1, 3, 5).reshape(B, gh*gw, C*p*p)`` in one kernel."""
+    lib = _cabi.load()
+    x = _dev(images, "images", torch.float16)
+    B, C, H, W = x.shape
+    out = torch.empty((B, (H // patch) * (W // patch), C * patch * patch), dtype=torch.float16, device=x.device)
+    _check(lib.arcq_patchify(x.data_ptr(), B, C, H, W, patch, out.data_ptr(), _stream()), "arcq_patchify")
+    return out
+
+
+def assemble_tokens(patches: torch.Tensor, cls_token: torch.Tensor, pos_embed: torch.Tensor) -> torch.Tensor:
+    """``torch.cat([cls_token.expand(B, 1, D), patches], dim=1) + pos_embed`` for fp16 tensors in one kernel;
+    patches [B, T, D], cls_token [1, 1, D], pos_embed [1, 1+T, D]."""
+    lib = _cabi.load()
+    p = _dev(patches, "patches", torch.float16)
+    B, T, D = p.shape
+    c = _dev(cls_token.reshape(-1), "cls_token", torch.float16)
+    e = _dev(pos_embed.reshape(-1, D), "pos_embed", torch.float16)
+    if c.numel() != D or tuple(e.shape) != (T + 1, D):
+        raise RuntimeError(f"cls_token {tuple(cls_token.shape)} / pos_embed {tuple(pos_embed.shape)} do not match patches {tuple(p.shape)}")
+    out = torch.empty((B, T + 1, D), dtype=torch.float16, device=p.device)
+    _check(lib.arcq_assemble_tokens(p.data_ptr(), c.data_ptr(), e.data_ptr(), B, T, D, out.data_ptr(), _stream()),
+           "arcq_assemble_tokens")
+    return out
+
+
 def unpack_codes_u8(packed: torch.Tensor, bits: int, length: int) -> torch.Tensor:
     """uint8 [R, ceil(length*bits/8)] -> uint8 [R, length] (reference: arcq_pack_kernel.cu:136-157)."""
     lib = _cabi.load()

@@ -96,7 +96,11 @@ class PatchEmbed(nn.Module):
         B, C, H, W = x.shape
         p = self.proj.kernel_size[0]
         gh, gw = H // p, W // p
-        patches = x.reshape(B, C, gh, p, gw, p).permute(0, 2, 4, 1, 3, 5).reshape(B, gh * gw, C * p * p)
+        if x.is_cuda and x.dtype == torch.float16 and p % 8 == 0 and H % p == 0 and W % p == 0:
+            from . import ops
+            patches = ops.patchify(x.contiguous(), p)          # the same matrix, gathered with 16-byte accesses
+        else:
+            patches = x.reshape(B, C, gh, p, gw, p).permute(0, 2, 4, 1, 3, 5).reshape(B, gh * gw, C * p * p)
         return F.linear(patches, self.proj.weight.reshape(self.proj.out_channels, -1), self.proj.bias)
 
 
@@ -121,7 +125,11 @@ class VisionTransformer(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x = self.patch_embed(x)
-        x = torch.cat([self.cls_token.expand(x.shape[0], -1, -1), x], dim=1) + self.pos_embed
+        if x.is_cuda and x.dtype == torch.float16 and x.shape[-1] % 8 == 0 and self.cls_token.dtype == torch.float16:
+            from . import ops
+            x = ops.assemble_tokens(x, self.cls_token, self.pos_embed)     # cat + add in one pass, same bits
+        else:
+            x = torch.cat([self.cls_token.expand(x.shape[0], -1, -1), x], dim=1) + self.pos_embed
         if x.is_cuda and x.dtype == torch.float16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 2048:
             return self._forward_fused_glue(x)
         for blk in self.blocks:

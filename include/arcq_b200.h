@@ -232,6 +232,18 @@ int arcq_attention_act_quant(const void* qkv, int64_t B, int64_t T, int64_t H, i
                              void* xhat, void* stream);
 
 /*
+ * The data movement around a ViT's patch-embedding GEMM (timm PatchEmbed.forward and VisionTransformer._pos_embed),
+ * fp16: arcq_patchify turns images [B, C, H, W] into the matrix [B*(H/patch)*(W/patch), C*patch*patch] whose
+ * product with the flattened convolution weight is the patch x patch, stride-patch convolution (patch a multiple
+ * of 8); arcq_assemble_tokens writes tokens [B, 1+T, D] = concat(class token [D], patches [B*T, D]) + position
+ * embedding [1+T, D], the sum rounded to fp16.  Pure data movement and one fp16 addition: bit-identical to the
+ * framework's reshape / permute / cat / add.
+ */
+int arcq_patchify(const void* images, int64_t B, int64_t C, int64_t H, int64_t W, int patch, void* rows, void* stream);
+int arcq_assemble_tokens(const void* patches, const void* cls_token, const void* pos_embed, int64_t B, int64_t T,
+                         int64_t D, void* tokens, void* stream);
+
+/*
  * Unpack codes to one byte per code.  Replaces unpack_codes_u8_cuda,
  * EXT/arcq_pack_kernel.cu:136-157 (kernel :74-90); the int64 variant
  * unpack_codes_cuda (:113-134) is this plus a widening on the host side.

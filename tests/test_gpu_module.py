@@ -203,3 +203,23 @@ def test_linear_forward_two_kernel_route_agrees_with_the_single_kernel(pkg, cuda
     assert float((y2.double() - ref).abs().max()) < 6e-3 * rms
     assert torch.equal(small, y2[:100])            # rows do not depend on the batch they are computed in
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("B,C,H,W,P", [(1, 3, 224, 224, 16), (5, 3, 224, 224, 16), (2, 1, 32, 64, 8), (3, 4, 48, 96, 24)])
+def test_patchify_and_token_assembly_equal_the_framework_ops(pkg, cuda_device, B, C, H, W, P):
+    """The two data-movement kernels around the patch-embedding GEMM: same bits as reshape / permute and cat / add."""
+    gen = torch.Generator().manual_seed(B + H + P)
+    x = torch.randn(B, C, H, W, generator=gen).half().to(cuda_device)
+    gh, gw = H // P, W // P
+    want = x.reshape(B, C, gh, P, gw, P).permute(0, 2, 4, 1, 3, 5).reshape(B, gh * gw, C * P * P)
+    assert torch.equal(pkg.ops.patchify(x, P), want)
+    D, T = 64 * 3, gh * gw
+    patches = torch.randn(B, T, D, generator=gen).half().to(cuda_device)
+    cls = torch.randn(1, 1, D, generator=gen).half().to(cuda_device)
+    pos = torch.randn(1, T + 1, D, generator=gen).half().to(cuda_device)
+    want = torch.cat([cls.expand(B, -1, -1), patches], dim=1) + pos
+    assert torch.equal(pkg.ops.assemble_tokens(patches, cls, pos), want)
+    with pytest.raises(RuntimeError):
+        pkg.ops.patchify(x, 7)
+    with pytest.raises(RuntimeError):
+        pkg.ops.assemble_tokens(patches, cls, pos[:, :-1])
