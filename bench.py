@@ -306,7 +306,7 @@ def launches_per_forward(pkg, a, n_lin: int, batch: int) -> int:
     merged = str(pkg.VisionTransformer.fuse_norm_quant) in ("auto", "1", "True") and dim in (192, 384, 768)
     norms = 2 * depth + 1
     quantizers = n_lin - (2 * depth if merged else 0)
-    return n_lin * (2 if staged else 1) + norms + quantizers
+    return n_lin * (2 if staged else 1) + norms + quantizers + 2        # + patch gathering and token assembly
 
 
 def _time_forward(runner, x, warm: int, iters: int) -> float:
