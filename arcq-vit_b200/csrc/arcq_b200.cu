@@ -78,7 +78,7 @@ enum Opt {
   O_WS_BN, O_WS_SA, O_WS_WS, O_WS_STATIONARY, O_WS_NBB, O_WS_GRID, O_WS_TMA_STORE, O_WS_ROTATE,
   O_ACT_QUANT_V1, O_ACT_QUANT_V2, O_LN_PLAIN,
   O_PAIR, O_PAIR_MIN_M, O_PAIR_BN, O_PAIR_SA, O_PAIR_KS, O_PAIR_NBB, O_PAIR_LUT, O_PAIR_PAIRS, O_PAIR_STATIONARY,
-  O_PAIR_WS, O_LNQ_SMALL, O_PDL, O_POLL_LIMIT, O_SPIN_LIMIT, O_COUNT
+  O_PAIR_WS, O_LNQ_SMALL, O_AQ2_MIN_GROUPS, O_PDL, O_POLL_LIMIT, O_SPIN_LIMIT, O_COUNT
 };
 struct OptDef { const char* name; int dflt; };
 const OptDef kOptDefs[O_COUNT] = {
@@ -87,7 +87,7 @@ const OptDef kOptDefs[O_COUNT] = {
     {"ARCQ_ACT_QUANT_V1", 0}, {"ARCQ_ACT_QUANT_V2", 0},   {"ARCQ_LN_PLAIN", 0},
     {"ARCQ_PAIR", 1},         {"ARCQ_PAIR_MIN_M", 1024},  {"ARCQ_PAIR_BN", 0},     {"ARCQ_PAIR_SA", 0},
     {"ARCQ_PAIR_KS", 0},      {"ARCQ_PAIR_NBB", 0},       {"ARCQ_PAIR_LUT", 0},    {"ARCQ_PAIR_PAIRS", 0},
-    {"ARCQ_PAIR_STATIONARY", -1}, {"ARCQ_PAIR_WS", 0}, {"ARCQ_LNQ_SMALL", 1}, {"ARCQ_PDL", 1},
+    {"ARCQ_PAIR_STATIONARY", -1}, {"ARCQ_PAIR_WS", 0}, {"ARCQ_LNQ_SMALL", 1}, {"ARCQ_AQ2_MIN_GROUPS", 0}, {"ARCQ_PDL", 1},
     {"ARCQ_POLL_LIMIT", 1 << 21}, {"ARCQ_SPIN_LIMIT", 1 << 25},
 };
 int g_opt[O_COUNT];
@@ -222,7 +222,8 @@ cudaError_t dispatch_act_quant_bits(int bits, const void* x, int x_dtype, long l
                                     int xhat_dtype, cudaStream_t st) {
   // The one-thread-per-group kernel needs enough groups to fill the machine (148 SMs x 4 blocks x 128
   // threads); below that the 8-lanes-per-group kernel has 8 times the parallelism and lower latency.
-  const bool enough = groups >= static_cast<long long>(sm_count()) * 4 * arcq::kAq2Threads / 2;
+  const long long min_groups = opt(O_AQ2_MIN_GROUPS) > 0 ? opt(O_AQ2_MIN_GROUPS) : static_cast<long long>(sm_count()) * 4 * arcq::kAq2Threads / 2;
+  const bool enough = groups >= min_groups;
   const bool v2 = enough && opt(O_ACT_QUANT_V1) == 0 && aligned(x, 16) &&
                   (packed == nullptr || aligned(packed, 16)) &&
                   (xhat == nullptr || (xhat_dtype == x_dtype && aligned(xhat, 16)));
@@ -1051,9 +1052,10 @@ int arcq_add_layernorm_act_quant(const void* x, const void* y, const float* gamm
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int G = static_cast<int>(K / 64);
   {
-    // Small inputs (the same bound below which the quantizer itself runs its eight-lanes-per-group form): the
-    // two-phase kernel whose results equal those of arcq_add_layernorm followed by arcq_act_quant bit for bit.
-    const bool small = M * G < static_cast<long long>(sm_count()) * 4 * arcq::kAq2Threads / 2 && opt(O_LNQ_SMALL) != 0;
+    // Small inputs, where the tiled kernel's 128-group tiles would not give every SM a block: the twelve-warp
+    // form (48 groups per block, lower latency).  Both forms give the same bits.  (DeiT-T at batch 64, 37 824
+    // groups, measured 8 % slower through the small form than through the tiled one.)
+    const bool small = M * G < static_cast<long long>(sm_count()) * arcq::kLnqThreads && opt(O_LNQ_SMALL) != 0;
     if (small) {
       const __half *xs = static_cast<const __half*>(x), *ys = static_cast<const __half*>(y);
       __half *so2 = static_cast<__half*>(sum_out), *ho2 = static_cast<__half*>(h_out), *xo2 = static_cast<__half*>(xhat);

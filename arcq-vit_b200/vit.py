@@ -108,7 +108,8 @@ class VisionTransformer(nn.Module):
     # The LayerNorm in front of qkv / fc1 also runs that layer's activation quantizer (one kernel instead of two, the
     # LayerNorm output never leaves the SM): "auto" / "1" wherever the merged kernel is built (rows of 192, 384 or 768
     # values), "0" never.  The merged kernel gives the same bits as the two separate kernels, so the switch changes
-    # timing only (DeiT-S batch 64: 1.96 -> 1.85 ms; batch 1: 0.525 -> 0.509 ms).
+    # timing only (DeiT-S batch 64: 1.96 -> 1.85 ms; batch 1: 0.525 -> 0.509 ms).  The library picks a low-latency form
+    # of the kernel for inputs of less than one 128-group tile per SM.
     fuse_norm_quant = os.environ.get("ARCQ_LN_QUANT", "auto")
 
     def __init__(self, dim: int, heads: int, depth: int, num_classes: int = 1000, img_size: int = 224,
