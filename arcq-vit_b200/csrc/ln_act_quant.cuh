@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(kLnqThreads, 4)
       float gg[3][8], bb[3][8];
       layernorm_lane_params<LANES>(gamma, beta, l, gg, bb);
       // (issuing the loads of all passes before the first pass computes was tried: 72 more live registers, spills,
-      // 13.5 us instead of 11.3 us)
+      // 13.5 us instead of 11.3 us; one pass ahead, with gamma and beta re-read per pass to make room: 11.4 us, no gain)
 #pragma unroll 1
       for (int pass = 0; pass < kPasses; ++pass) {
         const long long row = r_first + pass * kRowsPerPass + warp * kRowsPerWarp + sub;
