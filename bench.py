@@ -2,16 +2,19 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--model deit_small] [--bits 4] [--batch 64]
 
-A step is one forward of a batch of synthetic 224x224 images through the packed model (48 packed
-linears = 48 activation-quantise launches + 48 fused packed-GEMM launches, plus the floating-point
-glue).  With N > 1 (one process per GPU under torchrun) every rank runs its own batch (weak scaling)
-and the logits are all-gathered over NCCL each step.  Rank 0 prints one JSON line.
+A step is one forward of a batch of synthetic 224x224 images through the packed model: per packed linear
+(48 of them) one tcgen05 GEMM and one weight unpack on a side stream, an activation quantizer (merged with the
+preceding residual add + LayerNorm in front of qkv and fc1, with the GELU in front of fc2), plus the floating-point
+glue.  With N > 1 (one process per GPU under torchrun) every rank runs its own batch (weak scaling; `--global-batch`
+divides one batch over the ranks instead) and the logits are all-gathered over NCCL each step, on a side stream.
+Rank 0 prints one JSON line.
 
 `value` is timed with the batch already in HBM (CUDA-graph replay); `e2e` copies each step's batch
-from pinned host memory and reads the logits back inside the timed region.  `roofline` is the fused
-packed GEMM (the dominant kernel) timed alone on the model's four layer shapes; `cpu_baseline` is
-the CPU oracle port of the reference's fake-quant path on the host cores.  `--impl reference`
-prints the same line for that CPU path alone.
+from pinned host memory and reads the logits back inside the timed region.  `roofline` is the GEMM (the
+dominant kernel) on the model's four layer shapes; `cpu_baseline` is the reference's own CPU layer code
+(`baseline/_ref`, else the oracle port) on the host cores; `triton_baseline`, `bs1` and `memory` are the
+reference's Triton path and benchmark columns measured in the same run.  `--impl reference` prints the
+same line for the CPU path alone.
 """
 from __future__ import annotations
 
