@@ -16,7 +16,7 @@ DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 # every symbol include/arcq_b200.h declares
 EXPORTS = (
     "arcq_version", "arcq_last_error_string", "arcq_device_status", "arcq_debug_trace", "arcq_debug_set_option", "arcq_debug_get_option", "arcq_debug_wait_timeout", "arcq_act_quant", "arcq_gelu_act_quant", "arcq_packed_gemm", "arcq_packed_weight_gemm", "arcq_dense_weight_gemm", "arcq_packed_linear_static_scratch", "arcq_add_layernorm", "arcq_add_layernorm_act_quant", "arcq_attention", "arcq_attention_act_quant", "arcq_patchify", "arcq_assemble_tokens",
-    "arcq_unpack_codes", "arcq_pack_codes", "arcq_dequant", "arcq_unpack_weight_f16",
+    "arcq_unpack_codes", "arcq_pack_codes", "arcq_dequant", "arcq_unpack_weight_f16", "arcq_dense_weight_gemm_prefetch",
 )
 
 _lib = None
@@ -60,6 +60,7 @@ def load() -> ctypes.CDLL:
     lib.arcq_pack_codes.argtypes = [vp, i64, i64, ci, vp, vp]
     lib.arcq_dequant.argtypes = [vp, vp, vp, vp, vp, ci, ci, i64, i64, vp, ci, vp]
     lib.arcq_unpack_weight_f16.argtypes = [vp, vp, vp, vp, vp, ci, ci, i64, i64, vp, vp]
+    lib.arcq_dense_weight_gemm_prefetch.argtypes = [vp, vp, vp, i64, i64, i64, vp, ci, vp, vp, vp, vp, vp, ci, ci, i64, i64, vp, vp]
     for name in EXPORTS:
         getattr(lib, name)  # AttributeError here means header and library disagree
     _lib = lib

@@ -925,7 +925,8 @@ static int launch_pair_gemm(const PairConfig& cfg, const void* xhat, const void*
 }
 
 static int launch_pair_dense_gemm(const PairDenseConfig& cfg, const void* xhat, const void* w16, const float* bias,
-                                  int64_t M, int64_t N, int64_t K, void* y, int y_dtype, void* stream) {
+                                  int64_t M, int64_t N, int64_t K, void* y, int y_dtype, void* stream,
+                                  const arcq::UnpackWeightJob* next = nullptr) {
   CUtensorMap tm_a, tm_w, tm_y;
   if (!make_tensor_map_2d(&tm_a, xhat, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, static_cast<uint64_t>(M),
                           static_cast<uint64_t>(K), 64, arcq::kTileM, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -947,12 +948,30 @@ static int launch_pair_dense_gemm(const PairDenseConfig& cfg, const void* xhat, 
   p.spin_limit = static_cast<uint32_t>(opt(O_SPIN_LIMIT));
   p.status = status_ptr();
   if (p.status == nullptr) return fail(ARCQ_E_CUDA, "device status word not reachable");
-  if (cfg.stationary)
-    launch_pdl(arcq::dense_weight_gemm_pair_kernel<true>, static_cast<unsigned>(2 * cfg.pairs), arcq::kPairDenseThreads,
-               cfg.smem, static_cast<cudaStream_t>(stream), tm_a, tm_w, tm_y, p);
-  else
-    launch_pdl(arcq::dense_weight_gemm_pair_kernel<false>, static_cast<unsigned>(2 * cfg.pairs), arcq::kPairDenseThreads,
-               cfg.smem, static_cast<cudaStream_t>(stream), tm_a, tm_w, tm_y, p);
+  p.next = arcq::UnpackWeightJob{};
+  if (next != nullptr) p.next = *next;
+  const unsigned grid = static_cast<unsigned>(2 * cfg.pairs);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (next != nullptr) {
+    static thread_local int done_dev = -1;      // the prefetch form's shared-memory ceiling, once per (thread, device)
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (done_dev != dev) {
+      cudaFuncSetAttribute(arcq::dense_weight_gemm_pair_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kSmemBudget + 1024));
+      cudaFuncSetAttribute(arcq::dense_weight_gemm_pair_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kSmemBudget + 1024));
+      done_dev = dev;
+    }
+    if (cfg.stationary)
+      launch_pdl(arcq::dense_weight_gemm_pair_kernel<true, true>, grid, arcq::kPairDensePrefetchThreads, cfg.smem, st, tm_a, tm_w, tm_y, p);
+    else
+      launch_pdl(arcq::dense_weight_gemm_pair_kernel<false, true>, grid, arcq::kPairDensePrefetchThreads, cfg.smem, st, tm_a, tm_w, tm_y, p);
+  } else if (cfg.stationary) {
+    launch_pdl(arcq::dense_weight_gemm_pair_kernel<true>, grid, arcq::kPairDenseThreads, cfg.smem, st, tm_a, tm_w, tm_y, p);
+  } else {
+    launch_pdl(arcq::dense_weight_gemm_pair_kernel<false>, grid, arcq::kPairDenseThreads, cfg.smem, st, tm_a, tm_w, tm_y, p);
+  }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "dense_weight_gemm (pair) launch");
   return ARCQ_OK;
@@ -1002,6 +1021,43 @@ int arcq_dense_weight_gemm(const void* xhat, const void* w16, const float* bias,
   if (choose_pair_dense_config(M, N, K, y_dtype == ARCQ_DT_F32, &pc))
     return launch_pair_dense_gemm(pc, xhat, w16, bias, M, N, K, y, y_dtype, stream);
   return launch_ws_gemm(true, xhat, w16, nullptr, nullptr, nullptr, nullptr, bias, 4, M, N, K, y, y_dtype, stream);
+}
+
+int arcq_dense_weight_gemm_prefetch(const void* xhat, const void* w16, const float* bias, int64_t M, int64_t N,
+                                    int64_t K, void* y, int y_dtype, const uint8_t* next_packed, const float* next_mu,
+                                    const float* next_sigma, const float* next_codesum, const float* next_codebook,
+                                    int next_bits, int next_group_size, int64_t next_rows, int64_t next_K,
+                                    void* next_out, void* stream) {
+  if (!next_packed || !next_mu || !next_sigma || !next_codesum || !next_codebook || !next_out)
+    return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (next_bits < 2 || next_bits > 4) return fail(ARCQ_E_BAD_ARG, "bits must be 2, 3 or 4, got %d", next_bits);
+  if (next_group_size != 64) return fail(ARCQ_E_UNSUPPORTED, "group_size %d: only 64 is built", next_group_size);
+  if (next_rows <= 0 || next_K <= 0 || next_K % 64 != 0)
+    return fail(ARCQ_E_BAD_SHAPE, "bad shape of the next weight: rows=%lld K=%lld", (long long)next_rows, (long long)next_K);
+  if (!aligned(next_packed, 4) || !aligned(next_out, 16))
+    return fail(ARCQ_E_ALIGN, "next packed codes must be 4-byte, next_out 16-byte aligned");
+  if (!xhat || !w16 || !y) return fail(ARCQ_E_BAD_ARG, "null pointer argument");
+  if (y_dtype != ARCQ_DT_F16 && y_dtype != ARCQ_DT_F32) return fail(ARCQ_E_BAD_ARG, "y_dtype must be f16 or f32");
+  if (M < 0 || N <= 0 || K <= 0) return fail(ARCQ_E_BAD_SHAPE, "bad shape M=%lld N=%lld K=%lld", (long long)M,
+                                              (long long)N, (long long)K);
+  if (K % 64 != 0) return fail(ARCQ_E_UNSUPPORTED, "K=%lld: this entry point needs K %% 64 == 0", (long long)K);
+  if (N % 16 != 0) return fail(ARCQ_E_UNSUPPORTED, "N=%lld: this entry point needs N %% 16 == 0", (long long)N);
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > (1 << 20)) return fail(ARCQ_E_TOO_LARGE, "shape too large");
+  if (!aligned(xhat, 16) || !aligned(w16, 16) || !aligned(y, 16))
+    return fail(ARCQ_E_ALIGN, "xhat, w16 and y must be 16-byte aligned");
+  const arcq::UnpackWeightJob job = {next_packed, next_mu, next_sigma, next_codesum, next_codebook,
+                                     static_cast<__half*>(next_out), static_cast<long long>(next_rows),
+                                     static_cast<int>(next_K), next_bits};
+  PairDenseConfig pc;
+  if (M > 0 && choose_pair_dense_config(M, N, K, y_dtype == ARCQ_DT_F32, &pc))
+    return launch_pair_dense_gemm(pc, xhat, w16, bias, M, N, K, y, y_dtype, stream, &job);
+  // no pair configuration (or nothing to multiply): the GEMM by the one-CTA kernel, the unpack by its own kernel
+  if (M > 0) {
+    const int rc = launch_ws_gemm(true, xhat, w16, nullptr, nullptr, nullptr, nullptr, bias, 4, M, N, K, y, y_dtype, stream);
+    if (rc != ARCQ_OK) return rc;
+  }
+  return arcq_unpack_weight_f16(next_packed, next_mu, next_sigma, next_codesum, next_codebook, next_bits, next_group_size,
+                                next_rows, next_K, next_out, stream);
 }
 
 int arcq_add_layernorm(const void* x, const void* y, const float* gamma, const float* beta, float eps, int64_t M,

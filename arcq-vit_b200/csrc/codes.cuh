@@ -105,6 +105,64 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ packed, const float* 
 // cb16 = fp16(cb[c]) and one half-precision fused multiply-add: bit for bit the weight the packed-weight
 // GEMM kernels rebuild in shared memory, written out so that a dense GEMM can read it by TMA.
 // One thread per chunk of 8 codes (16 bytes of output); groups of 64.
+struct UnpackWeightJob {
+  const uint8_t* packed;     // null: nothing to do
+  const float* mu;
+  const float* sigma;
+  const float* codesum;
+  const float* codebook;
+  __half* out;
+  long long rows;
+  int K;
+  int bits;
+};
+
+// Chunks first, first + stride, ... of the job; `s_cb` holds the 16 codebook values in fp16.  Four chunks per
+// round, all their loads issued before the first result is used: a caller with few warps (the spare warps of a
+// GEMM kernel) has nothing else to hide the load latency with.
+template <int BITS>
+__device__ __forceinline__ void unpack_weight_f16_chunks(const UnpackWeightJob& j, const __half* s_cb, long long first,
+                                                         long long stride) {
+  const int chunks = j.K / 8;
+  const int G = j.K / 64;
+  const long long pc = static_cast<long long>(j.K) * BITS / 8;
+  const long long total = j.rows * chunks;
+  constexpr int U = 4;
+  for (long long i0 = first; i0 < total; i0 += U * stride) {
+    uint32_t w[U];
+    float sg[U], cs[U], mu[U];
+    long long off[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      const bool in = i < total;
+      const long long ii = in ? i : first;
+      const long long r = ii / chunks;
+      const int ch = static_cast<int>(ii - r * chunks);
+      const long long sgi = r * G + (ch >> 3);
+      w[u] = load_codes8<BITS>(j.packed + r * pc, ch);
+      sg[u] = __ldg(j.sigma + sgi);
+      cs[u] = __ldg(j.codesum + sgi);
+      mu[u] = __ldg(j.mu + sgi);
+      off[u] = in ? r * j.K + ch * 8 : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (off[u] < 0) continue;
+      const __half2 f2 = __floats2half2_rn(sg[u], fmaf(-sg[u], cs[u] * (1.0f / 64.0f), mu[u]));
+      const __half2 s2 = __low2half2(f2), m2 = __high2half2(f2);
+      uint32_t h[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const __half2 v2 = __halves2half2(s_cb[(w[u] >> (8 * q)) & 15u], s_cb[(w[u] >> (8 * q + 4)) & 15u]);
+        const __half2 r2 = __hfma2(s2, v2, m2);
+        h[q] = *reinterpret_cast<const uint32_t*>(&r2);
+      }
+      *reinterpret_cast<uint4*>(j.out + off[u]) = make_uint4(h[0], h[1], h[2], h[3]);
+    }
+  }
+}
+
 template <int BITS>
 __global__ void unpack_weight_f16_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ mu,
                                          const float* __restrict__ sigma, const float* __restrict__ codesum,
@@ -113,29 +171,9 @@ __global__ void unpack_weight_f16_kernel(const uint8_t* __restrict__ packed, con
   __shared__ __half s_cb[16];
   if (threadIdx.x < 16) s_cb[threadIdx.x] = __float2half_rn((threadIdx.x < (1 << BITS)) ? codebook[threadIdx.x] : 0.0f);
   __syncthreads();
-  const int chunks = K / 8;
-  const int G = K / 64;
-  const long long pc = static_cast<long long>(K) * BITS / 8;
-  const long long total = rows * chunks;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long r = i / chunks;
-    const int ch = static_cast<int>(i - r * chunks);
-    const int g = ch >> 3;
-    const uint32_t w = load_codes8<BITS>(packed + r * pc, ch);
-    const float sg = __ldg(sigma + r * G + g);
-    const __half2 f2 = __floats2half2_rn(sg, fmaf(-sg, __ldg(codesum + r * G + g) * (1.0f / 64.0f), __ldg(mu + r * G + g)));
-    const __half2 s2 = __low2half2(f2), m2 = __high2half2(f2);
-    uint32_t h[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const __half2 v2 = __halves2half2(s_cb[(w >> (8 * q)) & 15u], s_cb[(w >> (8 * q + 4)) & 15u]);
-      const __half2 r2 = __hfma2(s2, v2, m2);
-      h[q] = *reinterpret_cast<const uint32_t*>(&r2);
-    }
-    *reinterpret_cast<uint4*>(out + r * K + ch * 8) = make_uint4(h[0], h[1], h[2], h[3]);
-  }
+  const UnpackWeightJob j = {packed, mu, sigma, codesum, codebook, out, rows, K, BITS};
+  unpack_weight_f16_chunks<BITS>(j, s_cb, blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x,
+                                 static_cast<long long>(gridDim.x) * blockDim.x);
 }
-
 
 }  // namespace arcq

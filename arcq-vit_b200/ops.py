@@ -331,9 +331,14 @@ def pack_codes(codes: torch.Tensor, bits: int) -> torch.Tensor:
     return out
 
 
-def dense_weight_gemm(xhat: torch.Tensor, w16: torch.Tensor, bias, out_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+def dense_weight_gemm(xhat: torch.Tensor, w16: torch.Tensor, bias, out_dtype: torch.dtype = torch.float16,
+                      prefetch=None) -> torch.Tensor:
     """fp16 reconstructed activation [M,K] x fp16 weight [N,K] (+ fp32 bias) -> [M,N]: the ``F.linear`` of the
-    reference's on-the-fly forward (arcq_packed_on_the_fly.py:160) on the weight ``dequant`` wrote."""
+    reference's on-the-fly forward (arcq_packed_on_the_fly.py:160) on the weight ``unpack_weight_f16`` wrote.
+
+    ``prefetch = (packed, center, scale, code_sum, codebook, bits, group_size, out)``: also unpack that (the next
+    layer's) weight into the fp16 buffer ``out`` with spare warps of the same kernel; ``out`` must be a different
+    buffer from ``w16`` that no kernel still reads (see ``arcq_dense_weight_gemm_prefetch``)."""
     lib = _cabi.load()
     xhat = _dev(xhat, "xhat", torch.float16)
     w16 = _dev(w16, "w16", torch.float16)
@@ -350,6 +355,22 @@ def dense_weight_gemm(xhat: torch.Tensor, w16: torch.Tensor, bias, out_dtype: to
             raise RuntimeError("bias must have out_features entries")
     y = torch.empty((M, N), dtype=out_dtype, device=xhat.device)
     if M == 0:
+        if prefetch is not None:           # nothing to multiply, but the next layer still expects its weight
+            unpack_weight_f16(*prefetch[:7], out=prefetch[7])
+        return y
+    if prefetch is not None:
+        n_packed, n_mu, n_sg, n_cs, n_cb, n_bits, n_gs, n_out = prefetch
+        n_packed = _dev(n_packed, "next packed", torch.uint8)
+        n_mu, n_sg, n_cs, n_cb = (_dev(t, "next stats", torch.float32) for t in (n_mu, n_sg, n_cs, n_cb))
+        R, G = n_mu.shape
+        if (n_out.dtype != torch.float16 or not n_out.is_cuda or not n_out.is_contiguous() or n_out.numel() < R * G * n_gs
+                or n_out.data_ptr() == w16.data_ptr()):
+            raise RuntimeError("prefetch out must be a contiguous CUDA fp16 buffer of at least R*K elements, not w16 itself")
+        rc = lib.arcq_dense_weight_gemm_prefetch(xhat.data_ptr(), w16.data_ptr(), b.data_ptr() if b is not None else None,
+                                                 M, N, K, y.data_ptr(), _DT[out_dtype], n_packed.data_ptr(),
+                                                 n_mu.data_ptr(), n_sg.data_ptr(), n_cs.data_ptr(), n_cb.data_ptr(),
+                                                 n_bits, n_gs, R, G * n_gs, n_out.data_ptr(), _stream())
+        _check(rc, "arcq_dense_weight_gemm_prefetch")
         return y
     rc = lib.arcq_dense_weight_gemm(xhat.data_ptr(), w16.data_ptr(), b.data_ptr() if b is not None else None,
                                     M, N, K, y.data_ptr(), _DT[out_dtype], _stream())

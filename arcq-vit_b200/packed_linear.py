@@ -322,12 +322,13 @@ class ARCQPackedLinearOnTheFly(_KeepsFp32Metadata):
             # then weight unpack + contraction + bias (its steps 3-5) in one persistent kernel
             route = self._weight_route(x2.shape[0])
             if route == "staged":
-                w16, ready = self._stager.stage(self)     # starts the next layer's unpack on the side stream too
+                w16, ready, prefetch = self._stager.stage(self)     # also arranges the next layer's unpack
             x_hat = x2 if pre_quantized else ops.quantize_activation_dequant(
                 x2, self.activation_thresholds, self.activation_codebook, self.bits, self.group_size, torch.float16, pre_gelu)
             if route == "staged":
-                torch.cuda.current_stream(x2.device).wait_event(ready)
-                y = ops.dense_weight_gemm(x_hat, w16, bias, torch.float16)
+                if ready is not None:
+                    torch.cuda.current_stream(x2.device).wait_event(ready)
+                y = ops.dense_weight_gemm(x_hat, w16, bias, torch.float16, prefetch=prefetch)
                 self._stager.done(self)
             elif route == "dense":
                 w16 = ops.unpack_weight_f16(self.packed_weight_codes, self.weight_center, self.weight_scale,

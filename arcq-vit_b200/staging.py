@@ -2,9 +2,14 @@
 
 The reference's on-the-fly layer unpacks its weight into a shared fp16 scratch matrix and then calls a dense
 GEMM (fair_qat/arcq_packed_on_the_fly.py:147-160, scratch attached by
-scripts/benchmark_arcq_on_the_fly.py:189-191).  Here the same two steps run on two streams: the unpack of the
-next layer's weight goes to a side stream and into the other of two scratch matrices, so that by the time the
-next layer's activations are quantised its weight is already in L2 and the GEMM reads both operands by TMA.
+scripts/benchmark_arcq_on_the_fly.py:189-191).  Here the unpack of the next layer's weight goes into the other of
+two scratch matrices while the current layer computes, so that by the time the next layer's activations are
+quantised its weight is already in L2 and the GEMM reads both operands by TMA.  Two ways of running that unpack
+(``WeightStager.mode``): "stream" (default) -- its own kernel on a side stream, ordered by events; "inline" -- two
+spare warps of the current layer's GEMM kernel do it, no extra launch, stream or event.  Same bits either way; the
+inline form measured slower (DeiT-S batch 64: 1.825 ms against 1.80 ms, batch 1: 0.66 ms against 0.51 ms): two warps
+have nothing to hide their load latency with, the GEMM kernel cannot end before they do, and the two extra warps cost
+the GEMM itself a little.
 Nothing but the packed codes is kept between forwards; the scratch is two matrices of the largest layer.
 
 The order of the layers is their registration order in the model (timm's and this package's ViT register
@@ -17,6 +22,7 @@ threads need one model copy (and stager) per thread; the packed buffers can be s
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -30,6 +36,9 @@ class WeightStager:
     #: dense pair GEMM measured faster than the fused kernels at every batch size (DeiT-S batch 1 / 8 / 64:
     #: 0.55 / 0.74 / 2.00 ms against 0.67 / 0.91 / 2.24 ms)
     min_rows = 1
+    #: "stream": the next layer's weight is unpacked by its own kernel on a side stream; "inline": by spare warps of
+    #: this layer's GEMM kernel (measured slower, kept as a tested option)
+    mode = os.environ.get("ARCQ_STAGER_MODE", "stream")
 
     def __init__(self, model: nn.Module, layer_type: type):
         self.layers: List[nn.Module] = [m for m in model.modules() if isinstance(m, layer_type)]
@@ -46,12 +55,13 @@ class WeightStager:
         self._holds: List[Optional[int]] = [None, None]
         self._ready: List[Optional[torch.cuda.Event]] = [None, None]     # unpack into scratch b finished
         self._free: List[Optional[torch.cuda.Event]] = [None, None]      # the GEMM that read scratch b finished
+        self._side_used = False                                          # the side stream has work of this forward
 
     def _begin(self, module, args) -> None:
         self._reset()
 
     def _end(self, module, args, output) -> None:
-        if self._side is not None and any(h is not None for h in self._holds):
+        if self._side_used:
             torch.cuda.current_stream().wait_stream(self._side)     # nothing of the side stream outlives the forward
         self._reset()
 
@@ -79,22 +89,44 @@ class WeightStager:
         ev = torch.cuda.Event()
         ev.record(self._side)
         self._ready[b], self._holds[b] = ev, i
+        self._side_used = True
 
-    def stage(self, layer: nn.Module) -> Tuple[torch.Tensor, torch.cuda.Event]:
-        """(fp16 weight [N, K] of ``layer``, event to wait for before reading it).  Also starts the unpack of
-        the layer registered after it.  Call before the layer's activation quantizer is launched."""
+    def _unpack_here(self, i: int) -> None:
+        """Unpack layer i on the current stream (inline mode: the first layer of a forward, or a layer called out of
+        the registered order).  Stream order alone makes this safe: everything that read the matrix was launched
+        before."""
+        layer, b = self.layers[i], i & 1
+        buf = self._buffer(b, layer)
+        ops.unpack_weight_f16(layer.packed_weight_codes, layer.weight_center, layer.weight_scale, layer.weight_code_sum,
+                              layer.weight_codebook, layer.bits, layer.group_size, out=buf)
+        self._ready[b], self._holds[b] = None, i
+
+    def stage(self, layer: nn.Module):
+        """(fp16 weight [N, K] of ``layer``, event to wait for before reading it or None, prefetch argument for the
+        layer's GEMM or None).  Starts the unpack of the layer registered after it ("stream" mode) or describes it
+        for the GEMM to do ("inline" mode).  Call before the layer's activation quantizer is launched."""
         cur = torch.cuda.current_stream(layer.packed_weight_codes.device)
         i = layer._stage_index
         b = i & 1
+        inline = self.mode == "inline"
         if self._holds[b] != i:
-            self._unpack(i, cur)
+            self._unpack_here(i) if inline else self._unpack(i, cur)
+        prefetch = None
         if i + 1 < len(self.layers) and self._holds[(i + 1) & 1] != i + 1:
-            self._unpack(i + 1, cur)
+            if inline:
+                nxt = self.layers[i + 1]
+                prefetch = (nxt.packed_weight_codes, nxt.weight_center, nxt.weight_scale, nxt.weight_code_sum,
+                            nxt.weight_codebook, nxt.bits, nxt.group_size, self._buffer((i + 1) & 1, nxt))
+                self._ready[(i + 1) & 1], self._holds[(i + 1) & 1] = None, i + 1      # done by this layer's GEMM
+            else:
+                self._unpack(i + 1, cur)
         w16 = self._scratch[b][: layer.out_features * layer.in_features].view(layer.out_features, layer.in_features)
-        return w16, self._ready[b]
+        return w16, self._ready[b], prefetch
 
     def done(self, layer: nn.Module) -> None:
         """Call after the GEMM that reads the layer's staged weight has been launched."""
+        if self.mode == "inline":
+            return
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream(layer.packed_weight_codes.device))
         self._free[layer._stage_index & 1] = ev

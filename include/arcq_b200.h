@@ -281,6 +281,20 @@ int arcq_unpack_weight_f16(const uint8_t* packed, const float* mu, const float* 
                            const float* codebook, int bits, int group_size, int64_t rows, int64_t K,
                            void* out, void* stream);
 
+/*
+ * arcq_dense_weight_gemm that also unpacks the weight of the layer that runs NEXT (arcq_unpack_weight_f16 of
+ * next_packed ... into next_out) with two spare warps of every CTA while its own tiles run: the unpack then
+ * needs no launch, no second stream and no events.  next_out must not be w16 (use two scratch matrices in
+ * turn) and must not be read by any kernel launched after the one before the previous call of this function
+ * on the stream -- in a model that alternates two scratch matrices layer by layer this holds by construction:
+ * the matrix being overwritten was last read two GEMMs back.  Same results as the two separate calls.
+ */
+int arcq_dense_weight_gemm_prefetch(const void* xhat, const void* w16, const float* bias, int64_t M, int64_t N,
+                                    int64_t K, void* y, int y_dtype, const uint8_t* next_packed,
+                                    const float* next_mu, const float* next_sigma, const float* next_codesum,
+                                    const float* next_codebook, int next_bits, int next_group_size,
+                                    int64_t next_rows, int64_t next_K, void* next_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

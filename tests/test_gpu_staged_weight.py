@@ -78,16 +78,16 @@ def test_dense_pair_kernel_equals_the_one_cta_kernel(pkg, cuda_device, M, K, N, 
 
 @pytest.mark.parametrize("bits", [4, 3])
 def test_whole_model_logits_do_not_depend_on_the_weight_route(pkg, cuda_device, bits):
-    """DeiT-T at batch 8 (1576 rows: above the stager's row threshold): packed, dense on one stream, and staged on
-    two streams give the same logits, eagerly and replayed from a CUDA graph; the stager's scratch is two
-    matrices of the largest layer."""
+    """DeiT-T at batch 8: packed, dense on one stream, staged with the next layer's unpack inside the GEMM kernel, and
+    staged with it on a second stream give the same logits, eagerly and replayed from a CUDA graph; the stager's
+    scratch is two matrices of the largest layer."""
     dev = cuda_device
     gen = torch.Generator().manual_seed(5)
     model = pkg.create_vit("deit_tiny", seed=1).half().to(dev)
     x = torch.randn(8, 3, 224, 224, generator=gen).half().to(dev)
     x2 = torch.randn(8, 3, 224, 224, generator=gen).half().to(dev)
     cls = pkg.ARCQPackedLinearOnTheFly
-    saved = cls.weight_form
+    saved, saved_mode = cls.weight_form, pkg.WeightStager.mode
     try:
         with torch.no_grad():
             model = pkg.quantise_model(model, x, bits)
@@ -95,8 +95,10 @@ def test_whole_model_logits_do_not_depend_on_the_weight_route(pkg, cuda_device, 
             assert len(stager.layers) == 48 and all(m._stager is stager for m in stager.layers)
             assert pkg.attach_weight_stager(model) is stager            # idempotent
             want = {}
-            for form in ("packed", "dense", "staged", "auto"):
+            for form, mode in (("packed", "inline"), ("dense", "inline"), ("staged", "inline"), ("staged", "stream"),
+                               ("auto", "inline")):
                 cls.weight_form = form
+                pkg.WeightStager.mode = mode
                 y = model(x).clone()
                 y2 = model(x2).clone()
                 runner = pkg.GraphedModel(model, x)
@@ -107,7 +109,7 @@ def test_whole_model_logits_do_not_depend_on_the_weight_route(pkg, cuda_device, 
                 assert torch.equal(y, g) and torch.equal(y2, g2), form
                 if form == "packed":
                     want = {"y": y, "y2": y2}
-                assert torch.equal(y, want["y"]) and torch.equal(y2, want["y2"]), form
+                assert torch.equal(y, want["y"]) and torch.equal(y2, want["y2"]), (form, mode)
             assert stager.scratch_bytes() == 2 * 2 * 768 * 192
             # a layer called on its own, outside the model's forward, unpacks its weight when it is called
             cls.weight_form = "staged"
@@ -118,6 +120,7 @@ def test_whole_model_logits_do_not_depend_on_the_weight_route(pkg, cuda_device, 
             assert torch.equal(y_alone, layer(h))
     finally:
         cls.weight_form = saved
+        pkg.WeightStager.mode = saved_mode
 
 
 @pytest.mark.parametrize("M,K,bits", [(5, 192, 4), (300, 384, 4), (64 * 197, 384, 4), (64 * 197, 384, 3), (1000, 768, 4),
@@ -197,3 +200,41 @@ def test_model_with_the_fused_norm_quantizer(pkg, cuda_device):
             lin(torch.zeros(4, lin.in_features, dtype=torch.float16, device=dev), pre_gelu=True, pre_quantized=True)
     finally:
         pkg.VisionTransformer.fuse_norm_quant = saved
+
+
+@pytest.mark.parametrize("bits", [4, 3, 2])
+def test_dense_gemm_that_unpacks_the_next_weight(pkg, cuda_device, bits):
+    """``dense_weight_gemm(..., prefetch=...)``: the product is unchanged and the other scratch matrix holds the next
+    layer's weight, bit for bit what ``unpack_weight_f16`` writes; also with no rows to multiply and on the one-CTA
+    kernel."""
+    dev = cuda_device
+    gen = torch.Generator().manual_seed(70 + bits)
+    M, K, N = 3000, 384, 768
+    x = torch.randn(M, K, generator=gen).half().to(dev)
+    w = (torch.randn(N, K, generator=gen) * 0.05).half().to(dev)
+    b = torch.randn(N, generator=gen).to(dev)
+    K2, N2 = 768, 384
+    if not pkg.ops.packed_weight_gemm_supported(K2, N2, bits, 64):
+        pytest.skip("shape not taken")
+    pw, mw, sw, cw, cb, _ = _weight(pkg, dev, K2, N2, bits, seed=5 + bits)
+    want_w = pkg.ops.unpack_weight_f16(pw, mw, sw, cw, cb, bits, 64)
+    want_y = pkg.ops.dense_weight_gemm(x, w, b, torch.float16)
+    for options in (dict(), dict(ARCQ_PAIR=0), dict(ARCQ_PAIR_PAIRS=3)):
+        saved = {k: pkg._cabi.get_option(k) for k in options}
+        try:
+            for k, v in options.items():
+                pkg._cabi.set_option(k, v)
+            out = torch.full((N2 * K2 + 32,), float("nan"), dtype=torch.float16, device=dev)
+            y = pkg.ops.dense_weight_gemm(x, w, b, torch.float16, prefetch=(pw, mw, sw, cw, cb, bits, 64, out))
+        finally:
+            for k, v in saved.items():
+                pkg._cabi.set_option(k, v)
+        assert torch.equal(y, want_y), options
+        assert torch.equal(out[: N2 * K2].view(N2, K2), want_w), options
+        assert bool(torch.isnan(out[N2 * K2:]).all())
+    out = torch.zeros(N2 * K2, dtype=torch.float16, device=dev)
+    y0 = pkg.ops.dense_weight_gemm(x[:0], w, b, torch.float16, prefetch=(pw, mw, sw, cw, cb, bits, 64, out))
+    assert y0.shape[0] == 0 and torch.equal(out.view(N2, K2), want_w)
+    with pytest.raises(RuntimeError):
+        pkg.ops.dense_weight_gemm(x, w, b, torch.float16, prefetch=(pw, mw, sw, cw, cb, bits, 64, w.view(-1)))
+    assert pkg.ops.device_status() == 0
