@@ -964,9 +964,9 @@ static int launch_pair_dense_gemm(const PairDenseConfig& cfg, const void* xhat, 
       done_dev = dev;
     }
     if (cfg.stationary)
-      launch_pdl(arcq::dense_weight_gemm_pair_kernel<true, true>, grid, arcq::kPairDensePrefetchThreads, cfg.smem, st, tm_a, tm_w, tm_y, p);
+      launch_pdl(arcq::dense_weight_gemm_pair_kernel<true, true>, grid, arcq::kPairDenseThreads, cfg.smem, st, tm_a, tm_w, tm_y, p);
     else
-      launch_pdl(arcq::dense_weight_gemm_pair_kernel<false, true>, grid, arcq::kPairDensePrefetchThreads, cfg.smem, st, tm_a, tm_w, tm_y, p);
+      launch_pdl(arcq::dense_weight_gemm_pair_kernel<false, true>, grid, arcq::kPairDenseThreads, cfg.smem, st, tm_a, tm_w, tm_y, p);
   } else if (cfg.stationary) {
     launch_pdl(arcq::dense_weight_gemm_pair_kernel<true>, grid, arcq::kPairDenseThreads, cfg.smem, st, tm_a, tm_w, tm_y, p);
   } else {

@@ -6,15 +6,14 @@
 // Same pair geometry, barriers, epilogue and bounded waits as the packed-weight pair kernel (gemm_pair.cuh);
 // the difference is where the B operand comes from.  Both operands arrive by TMA: a stage holds this CTA's
 // 128 rows of A and its bn/2 rows of W16 for `ks` 64-wide K sub-tiles, and one barrier in the leader counts
-// the bytes of both CTAs.  There are no weight-building warps; a CTA is ten warps (twelve in the PREFETCH form):
+// the bytes of both CTAs.  There are no weight-building warps; a CTA is ten warps:
 //   warp 0      TMA: A and W16 sub-tiles of every stage
 //   warp 1      MMA issue (leader CTA only)
 //   warps 2-9   epilogue: tensor memory -> registers -> + bias -> fp16/fp32 -> staging -> TMA store
-//   warps 10-11 (PREFETCH form only, arcq_dense_weight_gemm_prefetch) unpack the NEXT layer's weight into the other
-//               scratch matrix while this layer's tiles run: no launch, no second stream, no events.  They wait for the
-//               previous kernel first, so the matrix they overwrite is no longer read by anybody (its last reader
-//               is two GEMMs back).  Measured slower than the unpack kernel on a side stream (two warps cannot hide
-//               their load latency and the kernel cannot end before they do), so the model does not use it by default.
+//               In the PREFETCH form (arcq_dense_weight_gemm_prefetch) they first unpack the NEXT layer's weight into
+//               the other scratch matrix, at a time when no accumulator is ready yet: no launch, no second stream,
+//               no events for the unpack.  They wait for the previous kernel first, so the matrix they overwrite is
+//               no longer read by anybody (its last reader is two GEMMs back).
 // and the kernel starts issuing as soon as its first stage has landed (no table or statistics set-up).
 //
 // STATIONARY: the pair's whole W16 slab (bn/2 rows x K per CTA) is loaded once and stays in shared memory for
@@ -46,9 +45,7 @@ struct PairDenseParams {
   UnpackWeightJob next;  // the weight of the layer that runs after this one, unpacked by two spare warps (or none)
 };
 
-constexpr int kPairDenseUnpackWarps = 2;
-constexpr int kPairDenseThreads = (2 + kPairEpiWarps) * 32;                                   // plain form
-constexpr int kPairDensePrefetchThreads = kPairDenseThreads + kPairDenseUnpackWarps * 32;     // with the unpack warps
+constexpr int kPairDenseThreads = (2 + kPairEpiWarps) * 32;
 // Staging blocks (2 KB: 32 rows x 64 bytes) per epilogue warp; a block can be rewritten once the TMA store that
 // reads it has done so.  Four blocks instead of two measured slower on every DeiT-S shape (qkv 13.6 -> 15.5 us,
 // fc2 17.5 -> 22.3 us): the 32 KB they take away from the operand stages cost more than deeper stores gain.  One
@@ -77,7 +74,7 @@ __host__ __device__ inline PairDenseSmem pair_dense_smem_layout(int bn, int sa, 
 }
 
 template <bool STATIONARY, bool PREFETCH = false>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PREFETCH ? kPairDensePrefetchThreads : kPairDenseThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairDenseThreads, 1)
     dense_weight_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                                   const __grid_constant__ CUtensorMap tm_y, const PairDenseParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -243,19 +240,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PREFETCH ? kPairDens
       __syncwarp();
       if (!ok && lane == 0) atomicExch(p.status, kStatusPairTimeout);
     }
-  } else if (PREFETCH && warp >= 2 + kPairEpiWarps) {
-    // ------------------------------------------------------------------ the next layer's weight
-    const int ut = tid - (2 + kPairEpiWarps) * 32;                 // 0 .. 63
-    if (p.next.packed != nullptr) {
-      if (ut < 16) s_next_cb[ut] = __float2half_rn(ut < (1 << p.next.bits) ? __ldg(p.next.codebook + ut) : 0.0f);
-      asm volatile("bar.sync 3, %0;" ::"n"(kPairDenseUnpackWarps * 32) : "memory");
-      pdl_wait();          // the scratch matrix being overwritten was last read two GEMMs back: complete by now
-      const long long first = static_cast<long long>(blockIdx.x) * (kPairDenseUnpackWarps * 32) + ut;
-      const long long stride = static_cast<long long>(gridDim.x) * (kPairDenseUnpackWarps * 32);
-      if (p.next.bits == 4) unpack_weight_f16_chunks<4>(p.next, s_next_cb, first, stride);
-      else if (p.next.bits == 3) unpack_weight_f16_chunks<3>(p.next, s_next_cb, first, stride);
-      else unpack_weight_f16_chunks<2>(p.next, s_next_cb, first, stride);
-    }
   } else {
     // ------------------------------------------------------------------ epilogue (own 128 rows of each tile)
     // Eight warps: two per tensor-memory lane quarter, taking alternate column steps of 64 bytes per row.
@@ -263,7 +247,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PREFETCH ? kPairDens
     // swizzle, conflict-free 16-byte stores) -> one TMA store.
     const int ew = warp - 2;
     for (int i = tid - 64; i < bn; i += kPairEpiWarps * 32) s_bias[i] = (p.bias != nullptr) ? __ldg(p.bias + n0 + i) : 0.0f;
-    asm volatile("bar.sync 2, %0;" ::"n"(kPairEpiWarps * 32) : "memory");   // bias table complete
+    if (PREFETCH && tid - 64 < 16)
+      s_next_cb[tid - 64] = __float2half_rn(tid - 64 < (1 << p.next.bits) ? __ldg(p.next.codebook + (tid - 64)) : 0.0f);
+    asm volatile("bar.sync 2, %0;" ::"n"(kPairEpiWarps * 32) : "memory");   // bias table (and codebook) complete
+    if (PREFETCH) {
+      // The next layer's weight, while these warps have no accumulator to drain yet.  Wait for the previous kernel
+      // first: the scratch matrix being overwritten was last read two GEMMs back and is then free for certain.
+      pdl_wait();
+      const long long first = static_cast<long long>(blockIdx.x) * (kPairEpiWarps * 32) + (tid - 64);
+      const long long stride = static_cast<long long>(gridDim.x) * (kPairEpiWarps * 32);
+      if (p.next.bits == 4) unpack_weight_f16_chunks<4>(p.next, s_next_cb, first, stride);
+      else if (p.next.bits == 3) unpack_weight_f16_chunks<3>(p.next, s_next_cb, first, stride);
+      else unpack_weight_f16_chunks<2>(p.next, s_next_cb, first, stride);
+    }
     const int lq = warp & 3;                          // tensor-memory lane quarter this warp may read
     const int half_id = ew >> 2;                      // which of the two warps of the quarter
     const uint32_t acc_empty_leader = mapa_shared(acc_empty, 0);

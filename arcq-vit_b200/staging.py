@@ -5,11 +5,11 @@ GEMM (fair_qat/arcq_packed_on_the_fly.py:147-160, scratch attached by
 scripts/benchmark_arcq_on_the_fly.py:189-191).  Here the unpack of the next layer's weight goes into the other of
 two scratch matrices while the current layer computes, so that by the time the next layer's activations are
 quantised its weight is already in L2 and the GEMM reads both operands by TMA.  Two ways of running that unpack
-(``WeightStager.mode``): "stream" (default) -- its own kernel on a side stream, ordered by events; "inline" -- two
-spare warps of the current layer's GEMM kernel do it, no extra launch, stream or event.  Same bits either way; the
-inline form measured slower (DeiT-S batch 64: 1.825 ms against 1.80 ms, batch 1: 0.66 ms against 0.51 ms): two warps
-have nothing to hide their load latency with, the GEMM kernel cannot end before they do, and the two extra warps cost
-the GEMM itself a little.
+(``WeightStager.mode``): "stream" (default) -- its own kernel on a side stream, ordered by events; "inline" -- the
+epilogue warps of the current layer's GEMM kernel do it before their first accumulator is ready, no extra launch,
+stream or event.  Same bits either way; the inline form measured slower at every batch size (DeiT-S batch 1 / 8 / 64:
+0.534 / 0.742 / 1.849 ms against 0.506 / 0.727 / 1.817 ms): the side stream hides the unpack completely, inside the
+GEMM it delays the first tile's drain.
 Nothing but the packed codes is kept between forwards; the scratch is two matrices of the largest layer.
 
 The order of the layers is their registration order in the model (timm's and this package's ViT register
@@ -36,8 +36,8 @@ class WeightStager:
     #: dense pair GEMM measured faster than the fused kernels at every batch size (DeiT-S batch 1 / 8 / 64:
     #: 0.55 / 0.74 / 2.00 ms against 0.67 / 0.91 / 2.24 ms)
     min_rows = 1
-    #: "stream": the next layer's weight is unpacked by its own kernel on a side stream; "inline": by spare warps of
-    #: this layer's GEMM kernel (measured slower, kept as a tested option)
+    #: "stream": the next layer's weight is unpacked by its own kernel on a side stream; "inline": by the epilogue
+    #: warps of this layer's GEMM kernel (measured slower, kept as a tested option)
     mode = os.environ.get("ARCQ_STAGER_MODE", "stream")
 
     def __init__(self, model: nn.Module, layer_type: type):
