@@ -15,7 +15,7 @@ DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 
 # every symbol include/arcq_b200.h declares
 EXPORTS = (
-    "arcq_version", "arcq_last_error_string", "arcq_device_status", "arcq_debug_trace", "arcq_debug_set_option", "arcq_debug_get_option", "arcq_debug_wait_timeout", "arcq_act_quant", "arcq_gelu_act_quant", "arcq_packed_gemm", "arcq_packed_weight_gemm", "arcq_dense_weight_gemm", "arcq_packed_linear_static_scratch", "arcq_add_layernorm", "arcq_add_layernorm_act_quant", "arcq_attention", "arcq_attention_act_quant", "arcq_patchify", "arcq_assemble_tokens",
+    "arcq_version", "arcq_last_error_string", "arcq_device_status", "arcq_debug_trace", "arcq_debug_set_option", "arcq_debug_get_option", "arcq_debug_last_gemm_kernel", "arcq_debug_wait_timeout", "arcq_act_quant", "arcq_gelu_act_quant", "arcq_packed_gemm", "arcq_packed_weight_gemm", "arcq_dense_weight_gemm", "arcq_packed_linear_static_scratch", "arcq_add_layernorm", "arcq_add_layernorm_act_quant", "arcq_attention", "arcq_attention_act_quant", "arcq_patchify", "arcq_assemble_tokens",
     "arcq_unpack_codes", "arcq_pack_codes", "arcq_dequant", "arcq_unpack_weight_f16", "arcq_dense_weight_gemm_prefetch",
 )
 
@@ -43,6 +43,7 @@ def load() -> ctypes.CDLL:
     lib.arcq_debug_trace.argtypes = [vp]
     lib.arcq_debug_set_option.argtypes = [ctypes.c_char_p, ci]
     lib.arcq_debug_get_option.argtypes = [ctypes.c_char_p, ctypes.POINTER(ci)]
+    lib.arcq_debug_last_gemm_kernel.argtypes = []
     lib.arcq_debug_wait_timeout.argtypes = [ctypes.c_uint, vp]
     lib.arcq_act_quant.argtypes = [vp, ci, i64, i64, vp, vp, ci, ci, vp, vp, vp, vp, vp, ci, vp]
     lib.arcq_gelu_act_quant.argtypes = lib.arcq_act_quant.argtypes
@@ -98,3 +99,11 @@ class option:
     def __exit__(self, *exc):
         set_option(self.name, self.old)
         return False
+
+
+GEMM_ONE_CTA_PACKED, GEMM_ONE_CTA_DENSE, GEMM_PAIR_PACKED, GEMM_PAIR_DENSE, GEMM_PAIR_DENSE_PREFETCH = 1, 2, 3, 4, 5
+
+
+def last_gemm_kernel() -> int:
+    """Which kernel form the last GEMM entry point called from this thread launched (see the header)."""
+    return int(load().arcq_debug_last_gemm_kernel())

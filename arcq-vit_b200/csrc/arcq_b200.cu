@@ -43,6 +43,8 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 __device__ int g_status_word = 0;
+// which GEMM kernel the last GEMM entry point of this host thread launched (arcq_debug_last_gemm_kernel)
+thread_local int g_last_gemm_kernel = 0;
 long long* g_trace_buf = nullptr;   // set by arcq_debug_trace; 64 timestamps per CTA
 
 int* status_ptr() {
@@ -677,6 +679,8 @@ int arcq_debug_set_option(const char* name, int value) {
   return fail(ARCQ_E_BAD_ARG, "unknown option %s", name);
 }
 
+int arcq_debug_last_gemm_kernel(void) { return g_last_gemm_kernel; }
+
 int arcq_debug_get_option(const char* name, int* value_out) {
   if (name == nullptr || value_out == nullptr) return fail(ARCQ_E_BAD_ARG, "null argument");
   load_options();
@@ -818,6 +822,7 @@ int arcq_packed_gemm(const uint8_t* packed_x, const float* mu_a, const float* si
 static int launch_ws_gemm(bool dense, const void* xhat, const void* w, const float* mu_w, const float* sigma_w,
                           const float* codesum_w, const float* w_codebook, const float* bias, int bits, int64_t M,
                           int64_t N, int64_t K, void* y, int y_dtype, void* stream) {
+  g_last_gemm_kernel = dense ? ARCQ_GEMM_ONE_CTA_DENSE : ARCQ_GEMM_ONE_CTA_PACKED;
   WsConfig cfg;
   if (!choose_ws_config(M, N, K, bits, dense, &cfg)) return fail(ARCQ_E_UNSUPPORTED, "no tile configuration for this shape");
 
@@ -919,6 +924,7 @@ static int launch_pair_gemm(const PairConfig& cfg, const void* xhat, const void*
   else if (bits == 3) ARCQ_LAUNCH_PAIR(3);
   else ARCQ_LAUNCH_PAIR(2);
 #undef ARCQ_LAUNCH_PAIR
+  g_last_gemm_kernel = ARCQ_GEMM_PAIR_PACKED;
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "packed_weight_gemm (pair) launch");
   return ARCQ_OK;
@@ -972,6 +978,7 @@ static int launch_pair_dense_gemm(const PairDenseConfig& cfg, const void* xhat, 
   } else {
     launch_pdl(arcq::dense_weight_gemm_pair_kernel<false>, grid, arcq::kPairDenseThreads, cfg.smem, st, tm_a, tm_w, tm_y, p);
   }
+  g_last_gemm_kernel = next != nullptr ? ARCQ_GEMM_PAIR_DENSE_PREFETCH : ARCQ_GEMM_PAIR_DENSE;
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "dense_weight_gemm (pair) launch");
   return ARCQ_OK;

@@ -82,6 +82,17 @@ int arcq_debug_set_option(const char* name, int value);
 int arcq_debug_get_option(const char* name, int* value_out);
 
 /*
+ * Which kernel the last GEMM entry point called by this host thread launched (0: none yet).  The entry points
+ * choose between kernel forms by shape and by what the device accepts (shared-memory ceiling, resident clusters)
+ * and fall back silently to a slower form; tests use this to pin the form the benchmark shapes must get.
+ */
+enum {
+  ARCQ_GEMM_ONE_CTA_PACKED = 1, ARCQ_GEMM_ONE_CTA_DENSE = 2, ARCQ_GEMM_PAIR_PACKED = 3, ARCQ_GEMM_PAIR_DENSE = 4,
+  ARCQ_GEMM_PAIR_DENSE_PREFETCH = 5
+};
+int arcq_debug_last_gemm_kernel(void);
+
+/*
  * Debugging aid: launches a one-warp kernel that waits, with the given poll limit (at most 65536), on a
  * barrier nothing ever arrives on.  The wait runs out, the kernel leaves the code 0x7E57 in the device status
  * word and returns: the path every bounded wait of the library takes instead of hanging.  Read the code with

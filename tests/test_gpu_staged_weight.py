@@ -238,3 +238,28 @@ def test_dense_gemm_that_unpacks_the_next_weight(pkg, cuda_device, bits):
     with pytest.raises(RuntimeError):
         pkg.ops.dense_weight_gemm(x, w, b, torch.float16, prefetch=(pw, mw, sw, cw, cb, bits, 64, w.view(-1)))
     assert pkg.ops.device_status() == 0
+
+
+@pytest.mark.parametrize("K,N", [(384, 1152), (384, 384), (384, 1536), (1536, 384), (768, 2304), (3072, 768)])
+def test_benchmark_shapes_get_the_pair_kernels(pkg, cuda_device, K, N):
+    """The entry points fall back to the one-CTA kernels when the device refuses a pair configuration (shared-memory
+    ceiling, resident clusters); results would stay right and the benchmark would quietly lose a third.  Pin the form
+    the DeiT layer shapes get at batch 64, for the dense, prefetching and packed entry points."""
+    dev, cabi = cuda_device, pkg._cabi
+    M, bits = 64 * 197, 4
+    pw, mw, sw, cw, cb, bias = _weight(pkg, dev, K, N, bits, seed=K + N)
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(1)).half().to(dev)
+    w16 = pkg.ops.unpack_weight_f16(pw, mw, sw, cw, cb, bits, 64)
+    pkg.ops.dense_weight_gemm(x, w16, bias, torch.float16)
+    assert cabi.last_gemm_kernel() == cabi.GEMM_PAIR_DENSE
+    other = torch.empty(N * K, dtype=torch.float16, device=dev)
+    pkg.ops.dense_weight_gemm(x, w16, bias, torch.float16, prefetch=(pw, mw, sw, cw, cb, bits, 64, other))
+    assert cabi.last_gemm_kernel() == cabi.GEMM_PAIR_DENSE_PREFETCH
+    pkg.ops.packed_weight_gemm(x, pw, mw, sw, cw, cb, bias, bits, 64, torch.float16)
+    assert cabi.last_gemm_kernel() == cabi.GEMM_PAIR_PACKED
+    pkg.ops.dense_weight_gemm(x[:197].contiguous(), w16, bias, torch.float16)        # batch 1 too
+    assert cabi.last_gemm_kernel() == cabi.GEMM_PAIR_DENSE
+    with cabi.option("ARCQ_PAIR", 0):
+        pkg.ops.dense_weight_gemm(x, w16, bias, torch.float16)
+        assert cabi.last_gemm_kernel() == cabi.GEMM_ONE_CTA_DENSE
+    assert pkg.ops.device_status() == 0
