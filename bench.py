@@ -295,10 +295,26 @@ def kernel_rooflines(pkg, a, dev, pk):
                                        else "packed: rebuilt inside the GEMM kernel",
                        "per_layer": per_layer}
     aq = aq_bytes / aq_ms / 1e6
+    # the form the model runs in front of qkv and fc1: residual add + LayerNorm + quantizer in one kernel (reads the
+    # residual stream and the branch output, writes the new residual stream and the reconstruction), against the
+    # two kernels it replaces, same harness
+    merged = None
+    dim = pkg.DEIT_CONFIGS[a.model][0]
+    if dim in (192, 384, 768):
+        norm = torch.nn.LayerNorm(dim, eps=1e-6).to(dev)
+        xs = [torch.randn(M, dim, generator=gen).half().to(dev) for _ in range(rot)]
+        ys = [torch.randn(M, dim, generator=gen).half().to(dev) for _ in range(rot)]
+        t_merged = timed(lambda i: pkg.ops.add_layernorm_quant(xs[i % rot], ys[i % rot], norm, th, cb, bits, 64))
+        t_apart = timed(lambda i: pkg.ops.quantize_activation_dequant(
+            pkg.ops.add_layernorm(xs[i % rot], ys[i % rot], norm)[1], th, cb, bits, 64, torch.float16))
+        mbytes = 4 * M * dim * 2
+        merged = {"kernel": "add_layernorm_act_quant_kernel", "ms": t_merged, "separate_kernels_ms": t_apart,
+                  "bytes": mbytes, "achieved": mbytes / t_merged / 1e6, "frac": mbytes / t_merged / 1e6 / pk["hbm_gbs"]}
     out["roofline_act_quant"] = {"kernel": "act_quant_v2_kernel (qkv / proj / fc1 inputs), act_quant_v4_kernel with GELU (fc2 input)", "bound": "hbm", "achieved": aq, "peak": pk["hbm_gbs"],
                                  "unit": "GB/s", "frac": aq / pk["hbm_gbs"], "traffic": None,
                                  "peak_source": pk["source"] + " copy",
-                                 "frac_of_same_size_copy": aq_copy_ms / aq_ms}
+                                 "frac_of_same_size_copy": aq_copy_ms / aq_ms,
+                                 "merged_with_layernorm": merged}
     return out
 
 
